@@ -1,0 +1,143 @@
+"""ctypes binding of the C ABI in include/ccglib_b200.h (harness for tests and benchmarks)."""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "lib", "libccglib_b200.so")
+
+# ccglib::ValueType (reference include/ccglib/common/value_type.h:14-22)
+INT1, INT32, BFLOAT16, FLOAT8E4M3, FLOAT8E5M2, FLOAT16, FLOAT32 = range(7)
+BASIC, OPT = 0, 1
+ROW_MAJOR, COL_MAJOR = 0, 1
+PLANAR, INTERLEAVED = 0, 1
+FORWARD, BACKWARD = 0, 1
+
+OK, INVALID_ARGUMENT, UNSUPPORTED, CUDA_ERROR, DEVICE_TIMEOUT, OUT_OF_MEMORY = range(6)
+
+EXPORTS = [
+    "ccglib_b200_gemm_dims", "ccglib_b200_gemm_plan_create", "ccglib_b200_gemm_run",
+    "ccglib_b200_gemm_plan_destroy", "ccglib_b200_gemm_plan_scratch_bytes",
+    "ccglib_b200_transpose_run", "ccglib_b200_pack_run", "ccglib_b200_device_status",
+    "ccglib_b200_status_string", "ccglib_b200_last_error",
+]
+
+
+class GemmDesc(ctypes.Structure):
+    _fields_ = [("batch", ctypes.c_size_t), ("m", ctypes.c_size_t), ("n", ctypes.c_size_t),
+                ("k", ctypes.c_size_t), ("type_in", ctypes.c_int), ("type_out", ctypes.c_int),
+                ("variant", ctypes.c_int), ("c_complex_axis", ctypes.c_int),
+                ("a_mem_order", ctypes.c_int), ("b_mem_order", ctypes.c_int),
+                ("c_mem_order", ctypes.c_int), ("alpha_re", ctypes.c_float),
+                ("alpha_im", ctypes.c_float), ("beta_re", ctypes.c_float),
+                ("beta_im", ctypes.c_float)]
+
+
+class Error(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__("ccglib_b200 status %d (%s): %s" % (status, STATUS_NAMES.get(status, "?"),
+                                                          message))
+        self.status = status
+        self.message = message
+
+
+STATUS_NAMES = {0: "OK", 1: "INVALID_ARGUMENT", 2: "UNSUPPORTED", 3: "CUDA_ERROR",
+                4: "DEVICE_TIMEOUT", 5: "OUT_OF_MEMORY"}
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load the CUDA library; raises if it has not been built (no fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("%s is missing: run `python -m ccglib_b200.build` "
+                              "(there is no CPU fallback)" % LIB_PATH)
+        L = ctypes.CDLL(LIB_PATH)
+        vp, sz, ci = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+        L.ccglib_b200_gemm_dims.argtypes = [ci, ci, ci, ctypes.POINTER(ctypes.c_uint * 3)]
+        L.ccglib_b200_gemm_dims.restype = ci
+        L.ccglib_b200_gemm_plan_create.argtypes = [ctypes.POINTER(GemmDesc), ctypes.POINTER(vp)]
+        L.ccglib_b200_gemm_plan_create.restype = ci
+        L.ccglib_b200_gemm_run.argtypes = [vp, vp, vp, vp, vp]
+        L.ccglib_b200_gemm_run.restype = ci
+        L.ccglib_b200_gemm_plan_destroy.argtypes = [vp]
+        L.ccglib_b200_gemm_plan_destroy.restype = ci
+        L.ccglib_b200_gemm_plan_scratch_bytes.argtypes = [vp]
+        L.ccglib_b200_gemm_plan_scratch_bytes.restype = sz
+        L.ccglib_b200_transpose_run.argtypes = [sz, sz, sz, sz, sz, sz, ci, vp, vp, vp]
+        L.ccglib_b200_transpose_run.restype = ci
+        L.ccglib_b200_pack_run.argtypes = [sz, ci, ci, vp, vp, vp]
+        L.ccglib_b200_pack_run.restype = ci
+        L.ccglib_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
+        L.ccglib_b200_device_status.restype = ci
+        L.ccglib_b200_status_string.argtypes = [ci]
+        L.ccglib_b200_status_string.restype = ctypes.c_char_p
+        L.ccglib_b200_last_error.argtypes = []
+        L.ccglib_b200_last_error.restype = ctypes.c_char_p
+        _lib = L
+    return _lib
+
+
+def _check(status: int) -> None:
+    if status != OK:
+        raise Error(status, lib().ccglib_b200_last_error().decode())
+
+
+def gemm_dims(type_in: int, type_out: int = FLOAT32, variant: int = OPT) -> tuple[int, int, int]:
+    dims = (ctypes.c_uint * 3)()
+    _check(lib().ccglib_b200_gemm_dims(type_in, type_out, variant, ctypes.byref(dims)))
+    return int(dims[0]), int(dims[1]), int(dims[2])
+
+
+class GemmPlan:
+    """Owns a ccglib_b200_gemm_plan (the counterpart of a ccglib::mma::GEMM object)."""
+
+    def __init__(self, batch, m, n, k, type_in, type_out, variant=OPT, c_complex_axis=PLANAR,
+                 c_mem_order=ROW_MAJOR, a_mem_order=ROW_MAJOR, b_mem_order=COL_MAJOR,
+                 alpha=(1.0, 0.0), beta=(0.0, 0.0)):
+        self.desc = GemmDesc(batch, m, n, k, type_in, type_out, variant, c_complex_axis,
+                             a_mem_order, b_mem_order, c_mem_order, alpha[0], alpha[1], beta[0],
+                             beta[1])
+        self._plan = ctypes.c_void_p()
+        _check(lib().ccglib_b200_gemm_plan_create(ctypes.byref(self.desc),
+                                                  ctypes.byref(self._plan)))
+
+    @property
+    def scratch_bytes(self) -> int:
+        return int(lib().ccglib_b200_gemm_plan_scratch_bytes(self._plan))
+
+    def run(self, d_a: int, d_b: int, d_c: int, stream: int = 0) -> None:
+        _check(lib().ccglib_b200_gemm_run(self._plan, d_a, d_b, d_c, stream))
+
+    def close(self) -> None:
+        if self._plan:
+            lib().ccglib_b200_gemm_plan_destroy(self._plan)
+            self._plan = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def transpose(batch, m, n, m_chunk, n_chunk, nr_bits, input_complex_axis, d_in, d_out,
+              stream: int = 0) -> None:
+    _check(lib().ccglib_b200_transpose_run(batch, m, n, m_chunk, n_chunk, nr_bits,
+                                           input_complex_axis, d_in, d_out, stream))
+
+
+def pack(n, direction, input_complex_axis, d_in, d_out, stream: int = 0) -> None:
+    _check(lib().ccglib_b200_pack_run(n, direction, input_complex_axis, d_in, d_out, stream))
+
+
+def device_status() -> int:
+    """Synchronise, then read and clear the device status word (0 = no device-side time-out)."""
+    word = ctypes.c_uint(0)
+    status = lib().ccglib_b200_device_status(ctypes.byref(word))
+    if status not in (OK, DEVICE_TIMEOUT):
+        _check(status)
+    return int(word.value)

@@ -1,0 +1,996 @@
+// Batched complex GEMM for sm_100a: C[b] = alpha * A[b] x B[b]^T + beta * C[b].
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer   -- stages [planes][rows][SW bytes] tiles of A and B in swizzled
+//                                 shared memory (one 3-D cp.async.bulk.tensor per operand)
+//   warp 1      MMA issuer     -- one thread issues tcgen05.mma; per 32-byte k-step four real MMAs
+//                                 Re += Ar.Br, Im += Ar.Bi, Im += Ai.Br, Re += (-Ai).Bi into two
+//                                 fp32 (or s32) accumulators in tensor memory
+//   warps 2..5  epilogue       -- tcgen05.ld the accumulators, apply alpha/beta, convert, and
+//                                 store planar/interleaved, row/col-major C
+// Stage hand-over uses mbarrier rings (full: TMA complete_tx, empty: tcgen05.commit); the
+// accumulator is handed to the epilogue by tcgen05.commit and back by thread arrivals.
+//
+// Every wait is bounded: a wait that runs out sets a shared abort flag and a bit in the global
+// status word, after which all roles fall through to the common tear-down (TMEM is always freed).
+//
+// Replaces the reference's wmma_complex_gemm_basic / wmma_complex_gemm_opt
+// (kernels/gemm_kernel_float.cu:35-355, kernels/gemm_kernel_int1.cu:64-356) and their
+// epilogues (kernels/matrix_operations.h:37-178).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace ccglib_b200 {
+
+// Sticky device-side status word: kernels OR a code into it when a bounded wait gives up.
+__device__ unsigned int g_device_status = 0;
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kBlockM = 128;       // rows of A per tile = TMEM lanes
+constexpr int kThreads = 192;      // producer warp, MMA warp, four epilogue warps
+constexpr int kTmemCols = 512;     // whole tensor memory of the SM
+constexpr int kMaxSmem = 227 * 1024;
+constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at boost clock
+
+enum CLayout { kPlanarRow = 0, kPlanarCol = 1, kInterRow = 2, kInterCol = 3 };
+
+struct GemmParams {
+  uint32_t M, N;
+  uint32_t k_blocks;   // k-blocks of SW bytes per tile
+  uint32_t tiles_m, tiles_n, group_n;
+  uint32_t num_tiles;
+  // operand coordinates
+  uint32_t tiled;          // 0: [batch][planes][rows][K] arrays, 1: slab layout of the opt variant
+  uint32_t k_per_slab;     // tiled: k-blocks per 128-byte slab row (128 / SW)
+  uint32_t slabs_k;        // tiled: slabs along K
+  uint32_t a_slabs_m;      // tiled: slabs along M
+  uint32_t b_slabs_n;      // tiled: slabs along N
+  uint32_t b_slab_rows;    // tiled: rows per B slab (n_blk of the layout contract)
+  uint32_t idesc, idesc_neg_a;
+  // epilogue
+  void *c;
+  uint32_t c_layout;
+  uint32_t have_alpha, have_beta, vec_ok;
+  float alpha_re, alpha_im, beta_re, beta_im;
+  unsigned int *status;
+};
+
+template <int BN, int SW, int A_PLANES> struct Cfg {
+  static constexpr int kAPlane = kBlockM * SW;
+  static constexpr int kBPlane = BN * SW;
+  static constexpr int kABytes = A_PLANES * kAPlane;
+  static constexpr int kBBytes = 2 * kBPlane;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kStagesRaw = (kMaxSmem - 1024 - kBarrierBytes) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kAccStages = (BN == 128) ? 2 : 1;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kBarrierBytes;
+  static_assert(kStages >= 2, "need at least two stages");
+  static_assert(2 * BN * kAccStages <= kTmemCols, "accumulators exceed tensor memory");
+};
+
+// Bounded wait on an mbarrier phase.  Returns false when the abort flag is up or the wait ran out
+// (in which case it raises the flag and records `code`).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          unsigned int *status, unsigned code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 0xFFu) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        atomicOr(status, code);
+        return false;
+      }
+    }
+  }
+}
+
+struct TileCoord {
+  uint32_t b, mt, nt;
+};
+
+// Tiles are walked batch by batch, and inside a batch item in column panels of `group_n` tiles
+// so that CTAs running at the same time share A row-blocks and B column-blocks in L2.
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, uint32_t tile) {
+  const uint32_t per_batch = p.tiles_m * p.tiles_n;
+  TileCoord t;
+  t.b = tile / per_batch;
+  const uint32_t r = tile - t.b * per_batch;
+  const uint32_t panel = p.group_n * p.tiles_m;
+  const uint32_t g = r / panel;
+  const uint32_t first_n = g * p.group_n;
+  const uint32_t width = min(p.group_n, p.tiles_n - first_n);
+  const uint32_t rr = r - g * panel;
+  t.mt = rr / width;
+  t.nt = first_n + (rr - t.mt * width);
+  return t;
+}
+
+template <typename T> struct OutTraits;
+template <> struct OutTraits<float> {
+  using Acc = float;
+  static __device__ __forceinline__ float from_bits(uint32_t u) { return __uint_as_float(u); }
+  static __device__ __forceinline__ float to_out(float v) { return v; }
+  static __device__ __forceinline__ float to_acc(float v) { return v; }
+};
+template <> struct OutTraits<__half> {
+  using Acc = float;
+  static __device__ __forceinline__ float from_bits(uint32_t u) { return __uint_as_float(u); }
+  static __device__ __forceinline__ __half to_out(float v) { return __float2half_rn(v); }
+  static __device__ __forceinline__ float to_acc(__half v) { return __half2float(v); }
+};
+template <> struct OutTraits<__nv_bfloat16> {
+  using Acc = float;
+  static __device__ __forceinline__ float from_bits(uint32_t u) { return __uint_as_float(u); }
+  static __device__ __forceinline__ __nv_bfloat16 to_out(float v) {
+    return __float2bfloat16_rn(v);
+  }
+  static __device__ __forceinline__ float to_acc(__nv_bfloat16 v) { return __bfloat162float(v); }
+};
+template <> struct OutTraits<int> {
+  using Acc = int;
+  static __device__ __forceinline__ int from_bits(uint32_t u) { return static_cast<int>(u); }
+  static __device__ __forceinline__ int to_out(int v) { return v; }
+  static __device__ __forceinline__ int to_acc(int v) { return v; }
+};
+
+// Pack two consecutive accumulator values into output words (one word per value for 32-bit
+// outputs, one word per pair for 16-bit outputs).
+template <typename OutT> struct Packer;
+template <> struct Packer<float> {
+  static constexpr int kPerWord = 1;
+  static __device__ __forceinline__ uint32_t word(const float *v) { return __float_as_uint(v[0]); }
+};
+template <> struct Packer<int> {
+  static constexpr int kPerWord = 1;
+  static __device__ __forceinline__ uint32_t word(const int *v) {
+    return static_cast<uint32_t>(v[0]);
+  }
+};
+template <> struct Packer<__half> {
+  static constexpr int kPerWord = 2;
+  static __device__ __forceinline__ uint32_t word(const float *v) {
+    const __half2 h = __floats2half2_rn(v[0], v[1]);
+    return *reinterpret_cast<const uint32_t *>(&h);
+  }
+};
+template <> struct Packer<__nv_bfloat16> {
+  static constexpr int kPerWord = 2;
+  static __device__ __forceinline__ uint32_t word(const float *v) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v[0], v[1]);
+    return *reinterpret_cast<const uint32_t *>(&h);
+  }
+};
+
+// Store `COUNT` consecutive output elements held in registers; 16-byte stores when allowed.
+template <typename OutT, int COUNT, typename Acc>
+__device__ __forceinline__ void store_run(OutT *dst, const Acc (&v)[COUNT], int valid, bool vec) {
+  using P = Packer<OutT>;
+  constexpr int kPerVec = 4 * P::kPerWord;
+  if (vec && valid == COUNT) {
+    uint4 *d = reinterpret_cast<uint4 *>(dst);
+#pragma unroll
+    for (int i = 0; i < COUNT / kPerVec; ++i) {
+      uint4 q;
+      q.x = P::word(&v[i * kPerVec + 0 * P::kPerWord]);
+      q.y = P::word(&v[i * kPerVec + 1 * P::kPerWord]);
+      q.z = P::word(&v[i * kPerVec + 2 * P::kPerWord]);
+      q.w = P::word(&v[i * kPerVec + 3 * P::kPerWord]);
+      d[i] = q;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < COUNT; ++i) {
+      if (i < valid) dst[i] = OutTraits<OutT>::to_out(v[i]);
+    }
+  }
+}
+
+// Epilogue for one row (m) and 32 consecutive columns starting at n0 of batch item b.
+template <typename OutT>
+__device__ __forceinline__ void epilogue_chunk(const GemmParams &p, uint32_t b, uint32_t m,
+                                               uint32_t n0, const uint32_t (&bits_re)[32],
+                                               const uint32_t (&bits_im)[32]) {
+  using Tr = OutTraits<OutT>;
+  using Acc = typename Tr::Acc;
+  if (m >= p.M) return;
+  OutT *C = static_cast<OutT *>(p.c);
+  const size_t M = p.M, N = p.N;
+  const int valid = static_cast<int>(min(32u, p.N - n0));
+  Acc re[32], im[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    re[j] = Tr::from_bits(bits_re[j]);
+    im[j] = Tr::from_bits(bits_im[j]);
+  }
+  if (p.have_alpha) {
+    const Acc ar = static_cast<Acc>(p.alpha_re), ai = static_cast<Acc>(p.alpha_im);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const Acc r = re[j];
+      re[j] = ar * r - ai * im[j];
+      im[j] = ai * r + ar * im[j];
+    }
+  }
+  // element offsets of (re, im) for column j
+  size_t base_re, stride_j, off_im;
+  switch (p.c_layout) {
+  case kPlanarRow:
+    base_re = ((size_t)b * 2 * M + m) * N + n0;
+    stride_j = 1;
+    off_im = M * N;
+    break;
+  case kPlanarCol:
+    base_re = ((size_t)b * 2 * N + n0) * M + m;
+    stride_j = M;
+    off_im = M * N;
+    break;
+  case kInterRow:
+    base_re = (((size_t)b * M + m) * N + n0) * 2;
+    stride_j = 2;
+    off_im = 1;
+    break;
+  default:
+    base_re = (((size_t)b * N + n0) * M + m) * 2;
+    stride_j = 2 * M;
+    off_im = 1;
+    break;
+  }
+  if (p.have_beta) {
+    const Acc br = static_cast<Acc>(p.beta_re), bi = static_cast<Acc>(p.beta_im);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (j < valid) {
+        const Acc cr = Tr::to_acc(C[base_re + j * stride_j]);
+        const Acc ci = Tr::to_acc(C[base_re + j * stride_j + off_im]);
+        re[j] += br * cr - bi * ci;
+        im[j] += bi * cr + br * ci;
+      }
+    }
+  }
+  if (p.c_layout == kPlanarRow) {
+    store_run<OutT, 32>(C + base_re, re, valid, p.vec_ok != 0);
+    store_run<OutT, 32>(C + base_re + off_im, im, valid, p.vec_ok != 0);
+  } else if (p.c_layout == kInterRow) {
+    Acc both[64];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      both[2 * j] = re[j];
+      both[2 * j + 1] = im[j];
+    }
+    store_run<OutT, 64>(C + base_re, both, 2 * valid, p.vec_ok != 0);
+  } else {
+    // column-major: consecutive lanes hold consecutive m, so each store is coalesced as is
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (j < valid) {
+        C[base_re + j * stride_j] = Tr::to_out(re[j]);
+        C[base_re + j * stride_j + off_im] = Tr::to_out(im[j]);
+      }
+    }
+  }
+}
+
+template <int KIND, int BN, int SW, int A_PLANES, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
+                     const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
+  using C = Cfg<BN, SW, A_PLANES>;
+  constexpr int kStages = C::kStages;
+  constexpr int kAccStages = C::kAccStages;
+  constexpr int kSub = SW / 32;  // 32-byte MMA k-steps per stage
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~static_cast<uintptr_t>(1023u));
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * C::kStageBytes);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * kStages;
+  const uint32_t bar_acc_full = bar_empty + 8 * kStages;
+  const uint32_t bar_acc_empty = bar_acc_full + 8 * kAccStages;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 2 * kAccStages);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  const uint32_t smem_base = smem_u32(smem);
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < kAccStages; ++s) {
+      mbar_init(bar_acc_full + 8 * s, 1);
+      mbar_init(bar_acc_empty + 8 * s, 128);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    uint32_t stage = 0, phase = 0;
+    uint32_t issued = 0;  // stages that have carried at least one load
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      const TileCoord t = decode_tile(p, tile);
+      for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+        if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status,
+                       kDevTimeoutProducer)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          int32_t ax, ay, az, bx, by, bz;
+          if (p.tiled) {
+            const uint32_t slab = kb / p.k_per_slab;
+            ax = bx = static_cast<int32_t>((kb - slab * p.k_per_slab) * SW);
+            ay = 0;
+            az = static_cast<int32_t>(2 * ((t.b * p.a_slabs_m + t.mt) * p.slabs_k + slab));
+            const uint32_t n_glob = t.nt * BN;
+            const uint32_t slab_n = n_glob / p.b_slab_rows;
+            by = static_cast<int32_t>(n_glob - slab_n * p.b_slab_rows);
+            bz = static_cast<int32_t>(2 * ((t.b * p.b_slabs_n + slab_n) * p.slabs_k + slab));
+          } else {
+            ax = bx = static_cast<int32_t>(kb * SW);
+            ay = static_cast<int32_t>(t.mt * kBlockM);
+            az = static_cast<int32_t>(t.b * A_PLANES);
+            by = static_cast<int32_t>(t.nt * BN);
+            bz = static_cast<int32_t>(t.b * 2);
+          }
+          const uint32_t full = bar_full + 8 * stage;
+          const uint32_t dst = smem_base + stage * C::kStageBytes;
+          mbar_arrive_expect_tx(full, C::kStageBytes);
+          tma_load_3d(dst, &tm_a, ax, ay, az, full);
+          tma_load_3d(dst + C::kABytes, &tm_b, bx, by, bz, full);
+        }
+        __syncwarp();
+        issued |= 1u << stage;
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    if (*abort_flag) {
+      // Do not leave the CTA while our own bulk copies may still be landing in its shared memory:
+      // wait (bounded) for the last load issued into every stage.
+      for (int s = 0; s < kStages; ++s) {
+        if (!(issued & (1u << s))) continue;
+        // stages before `stage` were last filled in the current phase, the others one phase back
+        const uint32_t last_parity = (static_cast<uint32_t>(s) < stage) ? phase : (phase ^ 1);
+        const long long t0 = clock64();
+        while (!mbar_try_wait(bar_full + 8 * s, last_parity)) {
+          if (clock64() - t0 > kWaitLimitCycles) {
+            atomicOr(p.status, kDevTimeoutDrain);
+            break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1, abort_flag, p.status,
+                     kDevTimeoutMma)) {
+        break;
+      }
+      tc_fence_after();
+      const uint32_t d_re = tmem_base + acc * (2 * BN);
+      const uint32_t d_im = d_re + BN;
+      for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kDevTimeoutMma)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_base = smem_base + stage * C::kStageBytes;
+          const uint32_t b_base = a_base + C::kABytes;
+#pragma unroll
+          for (int k = 0; k < kSub; ++k) {
+            const uint64_t a_re = smem_desc<SW>(a_base + k * 32);
+            const uint64_t a_im = smem_desc<SW>(a_base + C::kAPlane + k * 32);
+            const uint64_t b_re = smem_desc<SW>(b_base + k * 32);
+            const uint64_t b_im = smem_desc<SW>(b_base + C::kBPlane + k * 32);
+            const uint32_t accum = (kb | static_cast<uint32_t>(k)) != 0 ? 1u : 0u;
+            tc_mma<KIND>(d_re, a_re, b_re, p.idesc, accum);
+            tc_mma<KIND>(d_im, a_re, b_im, p.idesc, accum);
+            tc_mma<KIND>(d_im, a_im, b_re, p.idesc, 1u);
+            if constexpr (A_PLANES == 3) {
+              // third plane already holds -Ai (integer kinds have no negate bit)
+              const uint64_t a_neg = smem_desc<SW>(a_base + 2 * C::kAPlane + k * 32);
+              tc_mma<KIND>(d_re, a_neg, b_im, p.idesc, 1u);
+            } else {
+              tc_mma<KIND>(d_re, a_im, b_im, p.idesc_neg_a, 1u);
+            }
+          }
+          tc_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs have read it
+          if (kb + 1 == p.k_blocks) tc_commit(bar_acc_full + 8 * acc);
+        }
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (++acc == kAccStages) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const uint32_t quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+    uint32_t acc = 0, acc_phase = 0;
+    for (uint32_t tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+      const TileCoord t = decode_tile(p, tile);
+      if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, p.status,
+                     kDevTimeoutEpilogue)) {
+        break;
+      }
+      tc_fence_after();
+      const uint32_t m = t.mt * kBlockM + quad * 32 + lane;
+      const uint32_t t_re = tmem_base + ((quad * 32) << 16) + acc * (2 * BN);
+#pragma unroll 1
+      for (uint32_t c0 = 0; c0 < BN; c0 += 32) {
+        const uint32_t n0 = t.nt * BN + c0;
+        if (n0 >= p.N) break;
+        uint32_t bits_re[32], bits_im[32];
+        tmem_ld_32x32b_x32(t_re + c0, bits_re);
+        tmem_ld_32x32b_x32(t_re + BN + c0, bits_im);
+        tmem_wait_ld();
+        epilogue_chunk<OutT>(p, t.b, m, n0, bits_re, bits_im);
+      }
+      tc_fence_before();
+      mbar_arrive(bar_acc_empty + 8 * acc);
+      if (++acc == kAccStages) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ tear-down
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------ host side
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) !=
+            cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess) {
+      return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// Byte-typed 3-D tensor map: dims (row bytes, rows, slices), box (sw bytes, box_rows, box_slices).
+int make_map(CUtensorMap *tm, const void *base, uint64_t row_bytes, uint64_t rows, uint64_t slices,
+             uint64_t row_pitch, uint64_t slice_pitch, uint32_t sw, uint32_t box_rows,
+             uint32_t box_slices) {
+  EncodeTiledFn encode = get_encode_fn();
+  if (encode == nullptr) {
+    set_last_error("cuTensorMapEncodeTiled is not available from the installed driver");
+    return CCGLIB_B200_CUDA_ERROR;
+  }
+  const cuuint64_t dims[3] = {row_bytes, rows, slices};
+  const cuuint64_t strides[2] = {row_pitch, slice_pitch};
+  const cuuint32_t box[3] = {sw, box_rows, box_slices};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r = encode(
+      tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides, box,
+      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      sw == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+      sw == 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled failed with CUresult %d (row_bytes=%llu rows=%llu "
+                   "slices=%llu pitch=%llu)",
+                   static_cast<int>(r), (unsigned long long)row_bytes, (unsigned long long)rows,
+                   (unsigned long long)slices, (unsigned long long)row_pitch);
+    return CCGLIB_B200_CUDA_ERROR;
+  }
+  return CCGLIB_B200_OK;
+}
+
+using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const GemmParams);
+
+struct KernelEntry {
+  KernelFn fn;
+  int smem;
+};
+
+template <int KIND, int BN, int SW, int A_PLANES, typename OutT> KernelEntry entry() {
+  return {cgemm_tcgen05_kernel<KIND, BN, SW, A_PLANES, OutT>, Cfg<BN, SW, A_PLANES>::kSmemBytes};
+}
+
+template <int KIND, int A_PLANES, typename OutT> KernelEntry pick_tile(int bn, int sw) {
+  if (bn == 256) {
+    return sw == 128 ? entry<KIND, 256, 128, A_PLANES, OutT>()
+                     : entry<KIND, 256, 64, A_PLANES, OutT>();
+  }
+  return sw == 128 ? entry<KIND, 128, 128, A_PLANES, OutT>()
+                   : entry<KIND, 128, 64, A_PLANES, OutT>();
+}
+
+template <int KIND> KernelEntry pick_float_out(int type_out, int bn, int sw) {
+  switch (type_out) {
+  case CCGLIB_B200_FLOAT32:
+    return pick_tile<KIND, 2, float>(bn, sw);
+  case CCGLIB_B200_FLOAT16:
+    return pick_tile<KIND, 2, __half>(bn, sw);
+  case CCGLIB_B200_BFLOAT16:
+    return pick_tile<KIND, 2, __nv_bfloat16>(bn, sw);
+  default:
+    return {nullptr, 0};
+  }
+}
+
+int env_int(const char *name, int fallback) {
+  const char *v = std::getenv(name);
+  return (v != nullptr && *v != '\0') ? std::atoi(v) : fallback;
+}
+
+size_t type_bits(int t) {
+  switch (t) {
+  case CCGLIB_B200_INT1:
+    return 1;
+  case CCGLIB_B200_FLOAT8E4M3:
+  case CCGLIB_B200_FLOAT8E5M2:
+    return 8;
+  case CCGLIB_B200_BFLOAT16:
+  case CCGLIB_B200_FLOAT16:
+    return 16;
+  case CCGLIB_B200_INT32:
+  case CCGLIB_B200_FLOAT32:
+    return 32;
+  default:
+    return 0;
+  }
+}
+
+constexpr unsigned kSlabRowBytes = 128;  // bytes per slab row of the opt layout
+constexpr unsigned kSlabRowsA = 128;     // m_blk
+constexpr unsigned kSlabRowsB = 256;     // n_blk
+
+enum StageMode { kDirect = 0, kPadRows = 1, kExpandBits = 2 };
+
+} // namespace
+
+} // namespace ccglib_b200
+
+using namespace ccglib_b200;
+
+struct ccglib_b200_gemm_plan {
+  ccglib_b200_gemm_desc desc;
+  KernelEntry kernel;
+  int bn, sw, a_planes;
+  int stage_mode;
+  size_t k_bytes;         // bytes per operand row as the kernel reads it (before any padding)
+  size_t pitch;           // row pitch in bytes of what the kernel reads (basic layout)
+  size_t batch_chunk;     // batch items per kernel launch (== batch in direct mode)
+  void *scratch_a, *scratch_b;
+  size_t scratch_bytes;
+  size_t out_elem_bytes;
+  uint32_t idesc, idesc_neg_a;
+  int device;
+  int sms;
+};
+
+extern "C" int ccglib_b200_gemm_dims(int type_in, int type_out, int variant, unsigned dims[3]) {
+  (void)type_out;
+  (void)variant;
+  const size_t bits = type_bits(type_in);
+  if (dims == nullptr || bits == 0 || type_in == CCGLIB_B200_INT32) {
+    set_last_error("gemm_dims: unsupported input type %d", type_in);
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  dims[0] = kSlabRowsA;
+  dims[1] = kSlabRowsB;
+  dims[2] = static_cast<unsigned>(kSlabRowBytes * 8 / bits);
+  return CCGLIB_B200_OK;
+}
+
+extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
+                                            ccglib_b200_gemm_plan **out) {
+  if (desc == nullptr || out == nullptr) {
+    set_last_error("gemm_plan_create: null argument");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  *out = nullptr;
+  const ccglib_b200_gemm_desc &d = *desc;
+  if (d.batch == 0 || d.m == 0 || d.n == 0 || d.k == 0) {
+    set_last_error("gemm_plan_create: batch, M, N and K must be positive");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  if (d.m > 0x7FFFFFFFull || d.n > 0x7FFFFFFFull || d.k > 0x7FFFFFFFull ||
+      d.batch > 0x3FFFFFFFull) {
+    set_last_error("gemm_plan_create: dimension too large");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  if (d.variant != CCGLIB_B200_BASIC && d.variant != CCGLIB_B200_OPT) {
+    set_last_error("gemm_plan_create: unknown variant %d", d.variant);
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  if (d.variant == CCGLIB_B200_BASIC && d.c_complex_axis == CCGLIB_B200_INTERLEAVED) {
+    set_last_error("complex-interleaved output is not supported in basic variant");
+    return CCGLIB_B200_UNSUPPORTED;
+  }
+  if (d.a_mem_order != CCGLIB_B200_ROW_MAJOR) {
+    set_last_error("GEMM does not support col-major A matrix");
+    return CCGLIB_B200_UNSUPPORTED;
+  }
+  if (d.b_mem_order != CCGLIB_B200_COL_MAJOR) {
+    set_last_error("GEMM does not support row-major B matrix");
+    return CCGLIB_B200_UNSUPPORTED;
+  }
+
+  ccglib_b200_gemm_plan plan{};
+  plan.desc = d;
+  CCGLIB_CUDA_TRY(cudaGetDevice(&plan.device));
+  plan.sms = sm_count();
+  if (plan.sms <= 0) return CCGLIB_B200_CUDA_ERROR;
+  int cc_major = 0;
+  CCGLIB_CUDA_TRY(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, plan.device));
+  if (cc_major != 10) {
+    set_last_error("This architecture is not supported (need compute capability 10.x)");
+    return CCGLIB_B200_UNSUPPORTED;
+  }
+
+  // ---- kernel family and instruction descriptor
+  // idesc: [4,6) D format, [7,10) A format, [10,13) B format, bit 13 negate A, bit 15/16 majors
+  // (0 = K-major), [17,23) N>>3, [24,29) M>>4.
+  uint32_t d_fmt = 1, ab_fmt = 0;  // fp32 accumulate
+  int kind = kKindF16;
+  plan.a_planes = 2;
+  const size_t in_bits = type_bits(d.type_in);
+  switch (d.type_in) {
+  case CCGLIB_B200_FLOAT16:
+    kind = kKindF16;
+    ab_fmt = 0;
+    break;
+  case CCGLIB_B200_BFLOAT16:
+    kind = kKindF16;
+    ab_fmt = 1;
+    break;
+  case CCGLIB_B200_FLOAT32:
+    kind = kKindTF32;
+    ab_fmt = 2;
+    break;
+  case CCGLIB_B200_FLOAT8E4M3:
+    kind = kKindF8F6F4;
+    ab_fmt = 0;
+    break;
+  case CCGLIB_B200_FLOAT8E5M2:
+    kind = kKindF8F6F4;
+    ab_fmt = 1;
+    break;
+  case CCGLIB_B200_INT1:
+    kind = kKindI8;
+    ab_fmt = 1;  // signed 8-bit
+    d_fmt = 2;   // s32 accumulate
+    plan.a_planes = 3;
+    break;
+  default:
+    set_last_error("No kernel available for input type %d", d.type_in);
+    return CCGLIB_B200_UNSUPPORTED;
+  }
+  bool out_ok = false;
+  switch (d.type_in) {
+  case CCGLIB_B200_INT1:
+    out_ok = d.type_out == CCGLIB_B200_INT32;
+    break;
+  case CCGLIB_B200_FLOAT16:
+    out_ok = d.type_out == CCGLIB_B200_FLOAT32 || d.type_out == CCGLIB_B200_FLOAT16;
+    break;
+  case CCGLIB_B200_BFLOAT16:
+    out_ok = d.type_out == CCGLIB_B200_FLOAT32 || d.type_out == CCGLIB_B200_BFLOAT16;
+    break;
+  case CCGLIB_B200_FLOAT32:
+    out_ok = d.type_out == CCGLIB_B200_FLOAT32 || d.type_out == CCGLIB_B200_FLOAT16 ||
+             d.type_out == CCGLIB_B200_BFLOAT16;
+    break;
+  default:
+    out_ok = d.type_out == CCGLIB_B200_FLOAT32;
+    break;
+  }
+  if (!out_ok) {
+    set_last_error("Unsupported combination of input/output data types (%d -> %d)", d.type_in,
+                   d.type_out);
+    return CCGLIB_B200_UNSUPPORTED;
+  }
+  plan.out_elem_bytes = type_bits(d.type_out) / 8;
+
+  // ---- staging mode and operand geometry
+  if (d.type_in == CCGLIB_B200_INT1) {
+    plan.stage_mode = kExpandBits;
+    plan.k_bytes = d.k;  // one signed byte per sample after expansion
+    plan.pitch = ceil_div<size_t>(d.k, 16) * 16;
+  } else {
+    plan.k_bytes = d.k * in_bits / 8;
+    if (d.variant == CCGLIB_B200_OPT) {
+      plan.stage_mode = kDirect;
+      plan.pitch = kSlabRowBytes;
+    } else if (plan.k_bytes % 16 == 0) {
+      plan.stage_mode = kDirect;
+      plan.pitch = plan.k_bytes;
+    } else {
+      plan.stage_mode = kPadRows;
+      plan.pitch = ceil_div<size_t>(plan.k_bytes, 16) * 16;
+    }
+  }
+
+  // ---- tile shape
+  // BN = 256 halves the shared-memory traffic per flop; BN = 128 double-buffers the accumulators
+  // so the epilogue overlaps the next tile's main loop (short K) and gives more tiles (small M*N).
+  const size_t tiles_256 = d.batch * ceil_div<size_t>(d.m, kBlockM) * ceil_div<size_t>(d.n, 256);
+  int bn = (plan.k_bytes <= 2048 || tiles_256 < static_cast<size_t>(plan.sms)) ? 128 : 256;
+  int sw = 64;
+  bn = env_int("CCGLIB_B200_BN", bn);
+  sw = env_int("CCGLIB_B200_SW", sw);
+  if ((bn != 128 && bn != 256) || (sw != 64 && sw != 128)) {
+    set_last_error("CCGLIB_B200_BN must be 128 or 256 and CCGLIB_B200_SW 64 or 128");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  plan.bn = bn;
+  plan.sw = sw;
+  switch (kind) {
+  case kKindF16:
+    plan.kernel = pick_float_out<kKindF16>(d.type_out, bn, sw);
+    break;
+  case kKindTF32:
+    plan.kernel = pick_float_out<kKindTF32>(d.type_out, bn, sw);
+    break;
+  case kKindF8F6F4:
+    plan.kernel = pick_tile<kKindF8F6F4, 2, float>(bn, sw);
+    break;
+  default:
+    plan.kernel = pick_tile<kKindI8, 3, int>(bn, sw);
+    break;
+  }
+  if (plan.kernel.fn == nullptr) {
+    set_last_error("no kernel instance for this type combination");
+    return CCGLIB_B200_UNSUPPORTED;
+  }
+  plan.idesc = (d_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) |
+               (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+  plan.idesc_neg_a = plan.idesc | (1u << 13);
+  CCGLIB_CUDA_TRY(cudaFuncSetAttribute(reinterpret_cast<const void *>(plan.kernel.fn),
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       plan.kernel.smem));
+
+  // ---- scratch for the staged modes, processed in batch chunks of bounded size
+  plan.batch_chunk = d.batch;
+  if (plan.stage_mode != kDirect) {
+    const size_t per_item_a = plan.a_planes * d.m * plan.pitch;
+    const size_t per_item_b = 2 * d.n * plan.pitch;
+    const size_t budget = static_cast<size_t>(env_int("CCGLIB_B200_SCRATCH_MB", 2048)) << 20;
+    size_t chunk = budget / (per_item_a + per_item_b);
+    if (chunk < 1) chunk = 1;
+    if (chunk > d.batch) chunk = d.batch;
+    plan.batch_chunk = chunk;
+    plan.scratch_bytes = chunk * (per_item_a + per_item_b);
+    if (cudaMalloc(&plan.scratch_a, plan.scratch_bytes) != cudaSuccess) {
+      cudaGetLastError();
+      set_last_error("gemm_plan_create: could not allocate %zu bytes of staging scratch",
+                     plan.scratch_bytes);
+      return CCGLIB_B200_OUT_OF_MEMORY;
+    }
+    plan.scratch_b = static_cast<char *>(plan.scratch_a) + chunk * per_item_a;
+  }
+
+  *out = new (std::nothrow) ccglib_b200_gemm_plan(plan);
+  if (*out == nullptr) {
+    if (plan.scratch_a != nullptr) cudaFree(plan.scratch_a);
+    return CCGLIB_B200_OUT_OF_MEMORY;
+  }
+  return CCGLIB_B200_OK;
+}
+
+extern "C" size_t ccglib_b200_gemm_plan_scratch_bytes(const ccglib_b200_gemm_plan *plan) {
+  return plan != nullptr ? plan->scratch_bytes : 0;
+}
+
+extern "C" int ccglib_b200_gemm_plan_destroy(ccglib_b200_gemm_plan *plan) {
+  if (plan == nullptr) return CCGLIB_B200_OK;
+  if (plan->scratch_a != nullptr) cudaFree(plan->scratch_a);
+  delete plan;
+  return CCGLIB_B200_OK;
+}
+
+namespace {
+
+// Launch the GEMM kernel on `nb` batch items whose operands the kernel can read directly.
+int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b, void *c,
+                size_t nb, bool tiled, cudaStream_t stream) {
+  const ccglib_b200_gemm_desc &d = plan.desc;
+  GemmParams p{};
+  p.M = static_cast<uint32_t>(d.m);
+  p.N = static_cast<uint32_t>(d.n);
+  p.tiles_m = static_cast<uint32_t>(ceil_div<size_t>(d.m, kBlockM));
+  p.tiles_n = static_cast<uint32_t>(ceil_div<size_t>(d.n, plan.bn));
+  p.group_n = plan.bn == 256 ? 8 : 16;
+  const size_t tiles = nb * p.tiles_m * p.tiles_n;
+  if (tiles > 0x7FFFFFFFull) {
+    set_last_error("gemm_run: too many tiles");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  p.num_tiles = static_cast<uint32_t>(tiles);
+  p.tiled = tiled ? 1u : 0u;
+  CUtensorMap tm_a, tm_b;
+  int rc;
+  if (tiled) {
+    const size_t slabs_k = ceil_div<size_t>(plan.k_bytes, kSlabRowBytes);
+    const size_t slabs_m = ceil_div<size_t>(d.m, kSlabRowsA);
+    const size_t slabs_n = ceil_div<size_t>(d.n, kSlabRowsB);
+    p.k_per_slab = kSlabRowBytes / plan.sw;
+    p.slabs_k = static_cast<uint32_t>(slabs_k);
+    p.a_slabs_m = static_cast<uint32_t>(slabs_m);
+    p.b_slabs_n = static_cast<uint32_t>(slabs_n);
+    p.b_slab_rows = kSlabRowsB;
+    p.k_blocks = static_cast<uint32_t>(slabs_k * p.k_per_slab);
+    rc = make_map(&tm_a, a, kSlabRowBytes, kSlabRowsA, 2 * nb * slabs_m * slabs_k, kSlabRowBytes,
+                  kSlabRowBytes * kSlabRowsA, plan.sw, kBlockM, 2);
+    if (rc != CCGLIB_B200_OK) return rc;
+    rc = make_map(&tm_b, b, kSlabRowBytes, kSlabRowsB, 2 * nb * slabs_n * slabs_k, kSlabRowBytes,
+                  kSlabRowBytes * kSlabRowsB, plan.sw, plan.bn, 2);
+    if (rc != CCGLIB_B200_OK) return rc;
+  } else {
+    p.k_blocks = static_cast<uint32_t>(ceil_div<size_t>(plan.k_bytes, plan.sw));
+    rc = make_map(&tm_a, a, plan.k_bytes, d.m, plan.a_planes * nb, plan.pitch, plan.pitch * d.m,
+                  plan.sw, kBlockM, plan.a_planes);
+    if (rc != CCGLIB_B200_OK) return rc;
+    rc = make_map(&tm_b, b, plan.k_bytes, d.n, 2 * nb, plan.pitch, plan.pitch * d.n, plan.sw,
+                  plan.bn, 2);
+    if (rc != CCGLIB_B200_OK) return rc;
+  }
+  p.idesc = plan.idesc;
+  p.idesc_neg_a = plan.idesc_neg_a;
+  p.c = c;
+  const bool row = d.c_mem_order == CCGLIB_B200_ROW_MAJOR;
+  const bool planar = d.c_complex_axis == CCGLIB_B200_PLANAR;
+  p.c_layout = planar ? (row ? kPlanarRow : kPlanarCol) : (row ? kInterRow : kInterCol);
+  const bool is_int = d.type_in == CCGLIB_B200_INT1;
+  // the integer path always applies alpha and beta (as the reference CPU GEMM does), after
+  // truncating them to int
+  p.alpha_re = is_int ? static_cast<float>(static_cast<int>(d.alpha_re)) : d.alpha_re;
+  p.alpha_im = is_int ? static_cast<float>(static_cast<int>(d.alpha_im)) : d.alpha_im;
+  p.beta_re = is_int ? static_cast<float>(static_cast<int>(d.beta_re)) : d.beta_re;
+  p.beta_im = is_int ? static_cast<float>(static_cast<int>(d.beta_im)) : d.beta_im;
+  p.have_alpha = (p.alpha_re != 1.0f || p.alpha_im != 0.0f) ? 1u : 0u;
+  p.have_beta = (p.beta_re != 0.0f || p.beta_im != 0.0f) ? 1u : 0u;
+  // 16-byte stores need every row run to start on a 16-byte boundary
+  const size_t run_bytes = (planar ? d.n : 2 * d.n) * plan.out_elem_bytes;
+  p.vec_ok = (row && aligned16(c) && run_bytes % 16 == 0) ? 1u : 0u;
+  if (cudaGetSymbolAddress(reinterpret_cast<void **>(&p.status), g_device_status) != cudaSuccess) {
+    return cuda_fail(cudaGetLastError(), "cudaGetSymbolAddress(g_device_status)");
+  }
+  const unsigned grid = static_cast<unsigned>(tiles < static_cast<size_t>(plan.sms) ? tiles
+                                                                                   : plan.sms);
+  plan.kernel.fn<<<grid, kThreads, plan.kernel.smem, stream>>>(tm_a, tm_b, p);
+  CCGLIB_CUDA_TRY(cudaGetLastError());
+  return CCGLIB_B200_OK;
+}
+
+} // namespace
+
+extern "C" int ccglib_b200_gemm_run(ccglib_b200_gemm_plan *plan, const void *d_a, const void *d_b,
+                                    void *d_c, void *stream_v) {
+  if (plan == nullptr || d_a == nullptr || d_b == nullptr || d_c == nullptr) {
+    set_last_error("gemm_run: null argument");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const ccglib_b200_gemm_desc &d = plan->desc;
+  const bool tiled_in = d.variant == CCGLIB_B200_OPT;
+  if (plan->stage_mode == kDirect) {
+    if (!aligned16(d_a) || !aligned16(d_b)) {
+      set_last_error("gemm_run: A and B must be 16-byte aligned");
+      return CCGLIB_B200_INVALID_ARGUMENT;
+    }
+    return launch_gemm(*plan, d_a, d_b, d_c, d.batch, tiled_in, stream);
+  }
+  // Staged modes: re-stage a chunk of batch items into the plan's scratch, then multiply it.
+  const size_t c_item_bytes = 2 * d.m * d.n * plan->out_elem_bytes;
+  for (size_t b0 = 0; b0 < d.batch; b0 += plan->batch_chunk) {
+    const size_t nb = (d.batch - b0 < plan->batch_chunk) ? d.batch - b0 : plan->batch_chunk;
+    int rc;
+    if (plan->stage_mode == kExpandBits) {
+      const size_t words = ceil_div<size_t>(d.k, 32);
+      size_t a_item, b_item;
+      if (tiled_in) {
+        const size_t k_c_words = kSlabRowBytes / 4;
+        const size_t slabs_k = ceil_div<size_t>(words, k_c_words);
+        a_item = ceil_div<size_t>(d.m, kSlabRowsA) * slabs_k * 2 * kSlabRowsA * kSlabRowBytes;
+        b_item = ceil_div<size_t>(d.n, kSlabRowsB) * slabs_k * 2 * kSlabRowsB * kSlabRowBytes;
+      } else {
+        a_item = 2 * d.m * words * 4;
+        b_item = 2 * d.n * words * 4;
+      }
+      rc = launch_expand_bits(static_cast<const char *>(d_a) + b0 * a_item, plan->scratch_a, nb,
+                              d.m, d.k, plan->pitch, 3, tiled_in, kSlabRowsA, kSlabRowBytes * 8,
+                              stream);
+      if (rc != CCGLIB_B200_OK) return rc;
+      rc = launch_expand_bits(static_cast<const char *>(d_b) + b0 * b_item, plan->scratch_b, nb,
+                              d.n, d.k, plan->pitch, 2, tiled_in, kSlabRowsB, kSlabRowBytes * 8,
+                              stream);
+      if (rc != CCGLIB_B200_OK) return rc;
+    } else {
+      rc = launch_pad_rows(static_cast<const char *>(d_a) + b0 * 2 * d.m * plan->k_bytes,
+                           plan->scratch_a, nb * 2 * d.m, plan->k_bytes, plan->pitch, stream);
+      if (rc != CCGLIB_B200_OK) return rc;
+      rc = launch_pad_rows(static_cast<const char *>(d_b) + b0 * 2 * d.n * plan->k_bytes,
+                           plan->scratch_b, nb * 2 * d.n, plan->k_bytes, plan->pitch, stream);
+      if (rc != CCGLIB_B200_OK) return rc;
+    }
+    rc = launch_gemm(*plan, plan->scratch_a, plan->scratch_b,
+                     static_cast<char *>(d_c) + b0 * c_item_bytes, nb, false, stream);
+    if (rc != CCGLIB_B200_OK) return rc;
+  }
+  return CCGLIB_B200_OK;
+}
+
+extern "C" int ccglib_b200_device_status(unsigned *word) {
+  if (word == nullptr) {
+    set_last_error("device_status: null argument");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  CCGLIB_CUDA_TRY(cudaDeviceSynchronize());
+  unsigned value = 0;
+  CCGLIB_CUDA_TRY(cudaMemcpyFromSymbol(&value, g_device_status, sizeof(value)));
+  if (value != 0) {
+    const unsigned zero = 0;
+    CCGLIB_CUDA_TRY(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(zero)));
+    set_last_error("device status word 0x%x: a bounded device-side wait gave up", value);
+  }
+  *word = value;
+  return value == 0 ? CCGLIB_B200_OK : CCGLIB_B200_DEVICE_TIMEOUT;
+}
+

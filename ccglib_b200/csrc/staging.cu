@@ -1,0 +1,133 @@
+// Re-staging kernels used by the GEMM plan when the caller's operands cannot be read by TMA as
+// they are:
+//   * expand_bits: packed 1-bit samples (bit 1 = +1, bit 0 = -1) -> one signed byte per sample,
+//     planes (re, im[, -im]); tcgen05 has no 1-bit MMA and its integer kind has no negate bit,
+//     so the +-1 bytes (and the negated imaginary plane of A) are produced here.
+//   * pad_rows: copies rows whose byte length is not a multiple of 16 to a 16-byte pitch.
+// Both are pure data movement bounded by HBM bandwidth.
+#include "common.cuh"
+
+namespace ccglib_b200 {
+namespace {
+
+// 4 bits -> 4 bytes of 0/1 (bit i -> byte i).
+__device__ __forceinline__ uint32_t spread_nibble(uint32_t nibble) {
+  return (nibble * 0x00204081u) & 0x01010101u;
+}
+
+struct ExpandParams {
+  const uint32_t *in;
+  int8_t *out;
+  size_t batch, rows, k_bits, out_row_bytes;
+  size_t units;      // 32-byte output units (= input words) per row
+  size_t words;      // input words per row
+  int planes_out;    // 2: (re, im); 3: (re, im, -im)
+  int tiled;
+  size_t blk, kc_words, row_tiles, k_tiles;
+};
+
+__global__ void __launch_bounds__(256) expand_bits_kernel(const ExpandParams p) {
+  const size_t total = p.batch * 2 * p.rows * p.units;
+  for (size_t gid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; gid < total;
+       gid += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t u = gid % p.units;
+    size_t t = gid / p.units;
+    const size_t r = t % p.rows;
+    t /= p.rows;
+    const size_t c = t & 1;
+    const size_t b = t >> 1;
+    size_t src;
+    if (p.tiled) {
+      const size_t rt = r / p.blk, rr = r - rt * p.blk;
+      const size_t kt = u / p.kc_words, uu = u - kt * p.kc_words;
+      src = ((((b * p.row_tiles + rt) * p.k_tiles + kt) * 2 + c) * p.blk + rr) * p.kc_words + uu;
+    } else {
+      src = ((b * 2 + c) * p.rows + r) * p.words + u;
+    }
+    const uint32_t w = __ldg(p.in + src);
+    const size_t bit0 = u * 32;
+    const int valid = static_cast<int>(p.k_bits - bit0 < 32 ? p.k_bits - bit0 : 32);
+    uint32_t pos[8], neg[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t y = spread_nibble((w >> (4 * i)) & 0xFu);
+      uint32_t mask = 0xFFFFFFFFu;
+      if (4 * i + 4 > valid) mask = (4 * i >= valid) ? 0u : ((1u << (8 * (valid - 4 * i))) - 1u);
+      pos[i] = (0xFFFFFFFFu - y * 0xFEu) & mask;  // 1 -> 0x01, 0 -> 0xFF
+      neg[i] = (0x01010101u + y * 0xFEu) & mask;  // 1 -> 0xFF, 0 -> 0x01
+    }
+    const size_t plane_bytes = p.rows * p.out_row_bytes;
+    int8_t *dst = p.out + ((b * p.planes_out + c) * p.rows + r) * p.out_row_bytes + u * 32;
+    const bool second = u * 32 + 16 < p.out_row_bytes;  // the row pitch is a multiple of 16
+    *reinterpret_cast<uint4 *>(dst) = make_uint4(pos[0], pos[1], pos[2], pos[3]);
+    if (second) *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(pos[4], pos[5], pos[6], pos[7]);
+    if (c == 1 && p.planes_out == 3) {
+      int8_t *dn = dst + plane_bytes;
+      *reinterpret_cast<uint4 *>(dn) = make_uint4(neg[0], neg[1], neg[2], neg[3]);
+      if (second) *reinterpret_cast<uint4 *>(dn + 16) = make_uint4(neg[4], neg[5], neg[6], neg[7]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+pad_rows_kernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out, size_t rows,
+                size_t row_bytes, size_t out_row_bytes) {
+  const size_t vec_per_row = out_row_bytes / 16;
+  const size_t total = rows * vec_per_row;
+  for (size_t gid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; gid < total;
+       gid += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t r = gid / vec_per_row;
+    const size_t off = (gid - r * vec_per_row) * 16;
+    const uint8_t *src = in + r * row_bytes + off;
+    uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if (off + i < row_bytes) w[i >> 2] |= static_cast<uint32_t>(src[i]) << (8 * (i & 3));
+    }
+    *reinterpret_cast<uint4 *>(out + r * out_row_bytes + off) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+unsigned grid_for(size_t total, int threads) {
+  const size_t blocks = ceil_div<size_t>(total, threads);
+  const size_t cap = static_cast<size_t>(sm_count()) * 16;
+  return static_cast<unsigned>(blocks < cap ? (blocks ? blocks : 1) : cap);
+}
+
+} // namespace
+
+int launch_expand_bits(const void *d_in, void *d_out, size_t batch, size_t rows, size_t k_bits,
+                       size_t out_row_bytes, int planes_out, bool tiled, size_t blk,
+                       size_t k_c_bits, cudaStream_t stream) {
+  ExpandParams p{};
+  p.in = static_cast<const uint32_t *>(d_in);
+  p.out = static_cast<int8_t *>(d_out);
+  p.batch = batch;
+  p.rows = rows;
+  p.k_bits = k_bits;
+  p.out_row_bytes = out_row_bytes;
+  p.words = ceil_div<size_t>(k_bits, 32);
+  p.units = p.words;
+  p.planes_out = planes_out;
+  p.tiled = tiled ? 1 : 0;
+  p.blk = blk;
+  p.kc_words = k_c_bits / 32;
+  p.row_tiles = ceil_div<size_t>(rows, blk);
+  p.k_tiles = ceil_div<size_t>(p.words, p.kc_words);
+  const size_t total = batch * 2 * rows * p.units;
+  expand_bits_kernel<<<grid_for(total, 256), 256, 0, stream>>>(p);
+  CCGLIB_CUDA_TRY(cudaGetLastError());
+  return CCGLIB_B200_OK;
+}
+
+int launch_pad_rows(const void *d_in, void *d_out, size_t rows, size_t row_bytes,
+                    size_t out_row_bytes, cudaStream_t stream) {
+  const size_t total = rows * (out_row_bytes / 16);
+  pad_rows_kernel<<<grid_for(total, 256), 256, 0, stream>>>(
+      static_cast<const uint8_t *>(d_in), static_cast<uint8_t *>(d_out), rows, row_bytes,
+      out_row_bytes);
+  CCGLIB_CUDA_TRY(cudaGetLastError());
+  return CCGLIB_B200_OK;
+}
+
+} // namespace ccglib_b200

@@ -1,0 +1,145 @@
+/*
+ * ccglib_b200 -- C ABI of the B200 (sm_100a) complex-GEMM hot path.
+ *
+ * This is the boundary between host code (C++ classes mirroring the reference's
+ * ccglib::mma::GEMM, ccglib::transpose::Transpose, ccglib::packing::Packing and
+ * ccglib::pipeline::Pipeline, or any FFI) and the ahead-of-time compiled CUDA
+ * kernels.  Plain pointers, sizes and ints only; no C++ or framework types.
+ *
+ * Every function returns a ccglib_b200_status (0 = success).  Device pointers
+ * are passed as void* (the numeric value of a CUdeviceptr); streams as void*
+ * (the value of a CUstream / cudaStream_t; NULL = default stream).  A CUDA
+ * context must be current on the calling thread.  Functions that launch work
+ * are asynchronous on the given stream and never synchronise; only the plan
+ * constructor may allocate device memory.
+ *
+ * Integer codes of value types, variants, memory orders, complex-axis locations
+ * and directions are the enumerator values of the reference's public enums
+ * (include/ccglib/common/value_type.h:14-22, gemm/variant.h:6,
+ * gemm/mem_order.h:6, common/complex_order.h:12, common/direction.h:6).
+ */
+#ifndef CCGLIB_B200_H_
+#define CCGLIB_B200_H_
+
+#include <stddef.h>
+
+#if defined(__GNUC__)
+#define CCGLIB_B200_API __attribute__((visibility("default")))
+#else
+#define CCGLIB_B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ccglib_b200_status {
+  CCGLIB_B200_OK = 0,
+  CCGLIB_B200_INVALID_ARGUMENT = 1, /* bad size, pointer, alignment or enum value */
+  CCGLIB_B200_UNSUPPORTED = 2,      /* combination the library has no kernel for */
+  CCGLIB_B200_CUDA_ERROR = 3,       /* a CUDA runtime/driver call failed */
+  CCGLIB_B200_DEVICE_TIMEOUT = 4,   /* a bounded device-side wait gave up */
+  CCGLIB_B200_OUT_OF_MEMORY = 5     /* scratch allocation failed at plan creation */
+} ccglib_b200_status;
+
+enum { /* ccglib::ValueType */
+  CCGLIB_B200_INT1 = 0,
+  CCGLIB_B200_INT32 = 1,
+  CCGLIB_B200_BFLOAT16 = 2,
+  CCGLIB_B200_FLOAT8E4M3 = 3,
+  CCGLIB_B200_FLOAT8E5M2 = 4,
+  CCGLIB_B200_FLOAT16 = 5,
+  CCGLIB_B200_FLOAT32 = 6
+};
+enum { CCGLIB_B200_BASIC = 0, CCGLIB_B200_OPT = 1 };                /* ccglib::mma::Variant */
+enum { CCGLIB_B200_ROW_MAJOR = 0, CCGLIB_B200_COL_MAJOR = 1 };      /* ccglib::mma::MemOrder */
+enum { CCGLIB_B200_PLANAR = 0, CCGLIB_B200_INTERLEAVED = 1 };       /* ccglib::ComplexAxisLocation */
+enum { CCGLIB_B200_FORWARD = 0, CCGLIB_B200_BACKWARD = 1 };         /* ccglib::Direction */
+
+/*
+ * Problem description of one batched complex GEMM  C[b] = alpha * A[b] x B[b]^T + beta * C[b].
+ * Replaces the constructor arguments of ccglib::mma::GEMM
+ * (reference include/ccglib/gemm/mma.h:29-37, src/mma/GEMM.cpp:56-97), which the
+ * reference turns into NVRTC -D macros (src/mma/GEMM.cpp:133-214).
+ *
+ * Layouts (reference kernels/type_selector.h:224-241, kernels/gemm_kernel_float.cu:28-33):
+ *   basic A: [batch][2][M][K]   basic B: [batch][2][N][K]   (K contiguous; 1-bit: K/32 words)
+ *   opt   A: [batch][ceil(M/m_blk)][ceil(K/k_c)][2][m_blk][k_c], opt B likewise with n_blk,
+ *            zero padded, with (m_blk, n_blk, k_c) from ccglib_b200_gemm_dims
+ *   C planar:      [batch][2][M][N] (row-major) or [batch][2][N][M] (col-major)
+ *   C interleaved: [batch][M][N][2] (row-major) or [batch][N][M][2] (col-major)
+ */
+typedef struct ccglib_b200_gemm_desc {
+  size_t batch;
+  size_t m;
+  size_t n;
+  size_t k;           /* samples (bits for 1-bit input) */
+  int type_in;        /* value type of A and B */
+  int type_out;       /* value type of C */
+  int variant;        /* CCGLIB_B200_BASIC / CCGLIB_B200_OPT */
+  int c_complex_axis; /* CCGLIB_B200_PLANAR / CCGLIB_B200_INTERLEAVED */
+  int a_mem_order;    /* must be row-major */
+  int b_mem_order;    /* must be col-major */
+  int c_mem_order;
+  float alpha_re, alpha_im;
+  float beta_re, beta_im;
+} ccglib_b200_gemm_desc;
+
+typedef struct ccglib_b200_gemm_plan ccglib_b200_gemm_plan;
+
+/* Tile contract of the opt layout: dims = {m_blk, n_blk, k_c}.  Replaces
+ * ccglib::mma::GEMM::GetDimensions (reference src/mma/GEMM.cpp:270-275). */
+CCGLIB_B200_API int ccglib_b200_gemm_dims(int type_in, int type_out, int variant, unsigned dims[3]);
+
+/* Validate the description, choose the kernel and (only where the input needs re-staging:
+ * 1-bit input, or rows whose byte pitch is not a multiple of 16) allocate scratch.
+ * Replaces GEMM::Impl::Impl + compile_kernel (reference src/mma/GEMM.cpp:56-97,133-229).
+ * Errors the reference raises as exceptions come back as status codes: basic variant with
+ * interleaved C -> UNSUPPORTED (:77-80); col-major A or row-major B -> UNSUPPORTED (the
+ * reference fails in NVRTC, kernels/gemm_kernel_float.cu:20-25). */
+CCGLIB_B200_API int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc, ccglib_b200_gemm_plan **plan);
+
+/* Enqueue the GEMM.  Replaces ccglib::mma::GEMM::Run(CUdeviceptr a, b, c)
+ * (reference src/mma/GEMM.cpp:99-108,263-268). */
+CCGLIB_B200_API int ccglib_b200_gemm_run(ccglib_b200_gemm_plan *plan, const void *d_a, const void *d_b, void *d_c,
+                         void *stream);
+
+CCGLIB_B200_API int ccglib_b200_gemm_plan_destroy(ccglib_b200_gemm_plan *plan);
+
+/* Bytes of device scratch the plan owns (0 for the direct TMA path). */
+CCGLIB_B200_API size_t ccglib_b200_gemm_plan_scratch_bytes(const ccglib_b200_gemm_plan *plan);
+
+/*
+ * Tile transpose: [batch][2][M][N] (planar) or [batch][M][N][2] (interleaved) ->
+ * [batch][ceil(M/m_chunk)][ceil(N/n_chunk)][2][m_chunk][n_chunk], zero padded.  Elements are
+ * moved by width only: nr_bits in {8, 16, 32}, or 1 for 32-sample words (N and n_chunk then
+ * count samples and must be multiples of 32).  Replaces ccglib::transpose::Transpose::Run
+ * (reference src/transpose/Transpose.cpp:58-73, kernels/transpose_kernel.cu:50-82).
+ */
+CCGLIB_B200_API int ccglib_b200_transpose_run(size_t batch, size_t m, size_t n, size_t m_chunk, size_t n_chunk,
+                              size_t nr_bits, int input_complex_axis, const void *d_in,
+                              void *d_out, void *stream);
+
+/*
+ * Bit packing.  FORWARD: n one-byte samples -> ceil(n/32) words, sample i in bit i%32 of word
+ * i/32, set when the byte is non-zero; with interleaved input the buffer [n/2][2] is written
+ * as [2][n/2].  BACKWARD: words -> n bytes of 0/1 (planar only; interleaved -> UNSUPPORTED).
+ * Replaces ccglib::packing::Packing::Run (reference src/packing/Packing.cpp:44-74,
+ * kernels/packing_kernel.cu:7-62).
+ */
+CCGLIB_B200_API int ccglib_b200_pack_run(size_t n, int direction, int input_complex_axis, const void *d_in,
+                         void *d_out, void *stream);
+
+/* Read and clear the sticky device-side status word of the current device (synchronises the
+ * device).  Non-zero means a bounded wait inside a kernel gave up; its results are invalid. */
+CCGLIB_B200_API int ccglib_b200_device_status(unsigned *word);
+
+CCGLIB_B200_API const char *ccglib_b200_status_string(int status);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+CCGLIB_B200_API const char *ccglib_b200_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CCGLIB_B200_H_ */

@@ -1,0 +1,294 @@
+"""GPU parity tests of the complex GEMM, through the C ABI, against the CPU oracle.
+
+The cases re-express the reference's operator tests (test/gemm/mma.cpp: types :351-372, shapes
+:402-408 and :426-434, sections :442-520, alpha/beta :645-776; test/cuda/mma.cpp:87-94 all-ones
+known answer) and add the BASELINE configurations at sizes the oracle finishes in seconds."""
+import os
+
+import numpy as np
+import pytest
+
+import gpu_util as gu
+import oracle_util as ou
+from ccglib_b200 import capi
+
+pytestmark = pytest.mark.gpu
+
+FLOAT_TYPES = [(ou.E4M3, ou.F32), (ou.E5M2, ou.F32), (ou.F16, ou.F16), (ou.F32, ou.F16),
+               (ou.F16, ou.F32), (ou.F32, ou.F32), (ou.BF16, ou.F32), (ou.BF16, ou.BF16),
+               (ou.F32, ou.BF16)]
+TYPE_IDS = ["%s-%s" % (ou.TYPE_NAMES[i], ou.TYPE_NAMES[o]) for i, o in FLOAT_TYPES]
+SHAPES = [(128, 256, 64), (100, 60, 40)]  # aligned / unaligned, as in the reference
+SECTIONS = [  # (variant, complex axis of C, memory order of C)
+    (capi.BASIC, capi.PLANAR, capi.ROW_MAJOR),
+    (capi.BASIC, capi.PLANAR, capi.COL_MAJOR),
+    (capi.OPT, capi.PLANAR, capi.ROW_MAJOR),
+    (capi.OPT, capi.PLANAR, capi.COL_MAJOR),
+    (capi.OPT, capi.INTERLEAVED, capi.ROW_MAJOR),
+    (capi.OPT, capi.INTERLEAVED, capi.COL_MAJOR),
+]
+SECTION_IDS = ["basic-row", "basic-col", "opt-row", "opt-col", "opt-inter-row", "opt-inter-col"]
+
+
+def make_inputs(seed, type_in, B, M, N, K, dist="unit", scale=1.0):
+    rng = np.random.default_rng(seed)
+    if type_in == ou.INT1:
+        kw = (K + 31) // 32
+        a = ou.random_storage(rng, (B, 2, M, kw), ou.INT1)
+        b = ou.random_storage(rng, (B, 2, N, kw), ou.INT1)
+        pad = kw * 32 - K
+        if pad:
+            mask = np.uint32((1 << (32 - pad)) - 1)
+            a[..., -1] &= mask
+            b[..., -1] &= mask
+        return a, b
+    a = ou.random_storage(rng, (B, 2, M, K), type_in, dist, scale)
+    b = ou.random_storage(rng, (B, 2, N, K), type_in, dist, scale)
+    return a, b
+
+
+@pytest.mark.parametrize("section", SECTIONS, ids=SECTION_IDS)
+@pytest.mark.parametrize("shape", SHAPES, ids=["aligned", "unaligned"])
+@pytest.mark.parametrize("types", FLOAT_TYPES, ids=TYPE_IDS)
+def test_float_gemm_matches_oracle(types, shape, section):
+    type_in, type_out = types
+    M, N, K = shape
+    variant, c_axis, c_order = section
+    B = 3
+    a, b = make_inputs(11, type_in, B, M, N, K)
+    got = gu.run_gemm(type_in, type_out, a, b, B, M, N, K, variant=variant, c_axis=c_axis,
+                      c_order=c_order)
+    got = gu.canonical_c(got, B, M, N, c_axis, c_order)
+    want = gu.oracle_batch(type_in, type_out, a, b, B, M, N, K)
+    gu.assert_close_reference_rule(got, want, type_in, type_out)
+    gu.assert_close_fp64(got, type_in, type_out, a, b, K)
+
+
+def test_reference_fixture_batch16_f16():
+    # the reference fixture's batch size (test/gemm/mma.cpp:135)
+    B, M, N, K = 16, 128, 256, 64
+    a, b = make_inputs(12, ou.F16, B, M, N, K)
+    got = gu.run_gemm(ou.F16, ou.F32, a, b, B, M, N, K, variant=capi.OPT)
+    want = gu.oracle_batch(ou.F16, ou.F32, a, b, B, M, N, K, use_reference=True)
+    gu.assert_close_reference_rule(got.reshape(B, 2, M, N), want, ou.F16, ou.F32)
+    gu.assert_close_fp64(got.reshape(B, 2, M, N), ou.F16, ou.F32, a, b, K)
+
+
+@pytest.mark.parametrize("variant", [capi.BASIC, capi.OPT], ids=["basic", "opt"])
+@pytest.mark.parametrize("c_order", [capi.ROW_MAJOR, capi.COL_MAJOR], ids=["row", "col"])
+@pytest.mark.parametrize("shape", [(64, 64, 256), (100, 60, 288), (130, 300, 1056)],
+                         ids=["aligned", "unaligned", "multi-tile"])
+def test_int1_gemm_bit_exact(shape, c_order, variant):
+    M, N, K = shape
+    B = 3
+    a, b = make_inputs(13, ou.INT1, B, M, N, K)
+    got = gu.run_gemm(ou.INT1, ou.INT32, a, b, B, M, N, K, variant=variant, c_order=c_order)
+    got = gu.canonical_c(got, B, M, N, capi.PLANAR, c_order)
+    want = gu.oracle_batch(ou.INT1, ou.INT32, a, b, B, M, N, K)
+    assert np.array_equal(got, want)
+
+
+def test_int1_interleaved_output_and_k_padding():
+    # K not a multiple of 32: padding bits are zero and must not contribute
+    # (src/reference/GEMM.cpp:165-200)
+    B, M, N, K = 2, 40, 72, 70
+    a, b = make_inputs(14, ou.INT1, B, M, N, K)
+    want = gu.oracle_batch(ou.INT1, ou.INT32, a, b, B, M, N, K)
+    got = gu.run_gemm(ou.INT1, ou.INT32, a, b, B, M, N, K, variant=capi.BASIC)
+    assert np.array_equal(got.reshape(B, 2, M, N), want)
+    K = 96
+    a, b = make_inputs(15, ou.INT1, B, M, N, K)
+    want = gu.oracle_batch(ou.INT1, ou.INT32, a, b, B, M, N, K)
+    got = gu.run_gemm(ou.INT1, ou.INT32, a, b, B, M, N, K, variant=capi.OPT,
+                      c_axis=capi.INTERLEAVED)
+    assert np.array_equal(gu.canonical_c(got, B, M, N, capi.INTERLEAVED, capi.ROW_MAJOR), want)
+
+
+@pytest.mark.parametrize("M", [255, 256])
+def test_alpha_beta_f16(M):
+    # test/gemm/mma.cpp:645-700
+    B, N, K = 2, 128, 256
+    alpha, beta = (0.3, 1.6), (0.8, -1.1)
+    a, b = make_inputs(16, ou.F16, B, M, N, K)
+    rng = np.random.default_rng(17)
+    c0 = rng.random((B, 2, M, N), dtype=np.float32)
+    got = gu.run_gemm(ou.F16, ou.F32, a, b, B, M, N, K, variant=capi.BASIC, alpha=alpha, beta=beta,
+                      c0=c0)
+    want = gu.oracle_batch(ou.F16, ou.F32, a, b, B, M, N, K, alpha, beta, c0)
+    gu.assert_close_reference_rule(got.reshape(B, 2, M, N), want, ou.F16, ou.F32)
+    # tighter: alpha/beta are applied in float32 on a float32 accumulator
+    assert np.allclose(got.reshape(B, 2, M, N), want, rtol=2e-5, atol=2e-3)
+
+
+@pytest.mark.parametrize("section", [(capi.OPT, capi.INTERLEAVED, capi.COL_MAJOR),
+                                     (capi.OPT, capi.PLANAR, capi.COL_MAJOR),
+                                     (capi.OPT, capi.INTERLEAVED, capi.ROW_MAJOR)],
+                         ids=["inter-col", "planar-col", "inter-row"])
+def test_alpha_beta_f16_out_layouts(section):
+    variant, c_axis, c_order = section
+    B, M, N, K = 2, 100, 60, 40
+    alpha, beta = (0.5, 2.5), (0.25, -1.5)
+    a, b = make_inputs(18, ou.F16, B, M, N, K)
+    rng = np.random.default_rng(19)
+    c0 = ou.quantize(rng.random((B, 2, M, N), dtype=np.float32), ou.F16)  # canonical
+    # lay c0 out the way the GEMM will read it
+    if c_axis == capi.PLANAR:
+        c0_dev = c0.transpose(0, 1, 3, 2) if c_order == capi.COL_MAJOR else c0
+    else:
+        c0_dev = c0.transpose(0, 3, 2, 1) if c_order == capi.COL_MAJOR else c0.transpose(0, 2, 3, 1)
+    got = gu.run_gemm(ou.F16, ou.F16, a, b, B, M, N, K, variant=variant, c_axis=c_axis,
+                      c_order=c_order, alpha=alpha, beta=beta, c0=np.ascontiguousarray(c0_dev))
+    got = gu.canonical_c(got, B, M, N, c_axis, c_order)
+    want = gu.oracle_batch(ou.F16, ou.F16, a, b, B, M, N, K, alpha, beta, c0)
+    gu.assert_close_reference_rule(got, want, ou.F16, ou.F16)
+
+
+def test_alpha_beta_int1():
+    # test/gemm/mma.cpp:702-776
+    B, M, N, K = 2, 256, 128, 256
+    alpha, beta = (2.0, 3.0), (-1.0, 2.0)
+    a, b = make_inputs(20, ou.INT1, B, M, N, K)
+    rng = np.random.default_rng(21)
+    c0 = rng.integers(-100, 100, size=(B, 2, M, N), dtype=np.int32)
+    got = gu.run_gemm(ou.INT1, ou.INT32, a, b, B, M, N, K, variant=capi.BASIC, alpha=alpha,
+                      beta=beta, c0=c0)
+    want = gu.oracle_batch(ou.INT1, ou.INT32, a, b, B, M, N, K, alpha, beta, c0)
+    assert np.array_equal(got.reshape(B, 2, M, N), want)
+
+
+@pytest.mark.parametrize("type_in", [ou.F16, ou.BF16, ou.F32, ou.E4M3, ou.E5M2, ou.INT1],
+                         ids=lambda t: ou.TYPE_NAMES[t])
+def test_all_ones_known_answer(type_in):
+    # all-ones input: Re = K - K = 0, Im = 2K (test/cuda/mma.cpp:87-94)
+    B, M, N, K = 2, 128, 64, 256
+    type_out = ou.INT32 if type_in == ou.INT1 else ou.F32
+    if type_in == ou.INT1:
+        a = np.full((B, 2, M, K // 32), 0xFFFFFFFF, np.uint32)
+        b = np.full((B, 2, N, K // 32), 0xFFFFFFFF, np.uint32)
+    else:
+        a = ou.quantize(np.ones((B, 2, M, K), np.float32), type_in)
+        b = ou.quantize(np.ones((B, 2, N, K), np.float32), type_in)
+    got = gu.run_gemm(type_in, type_out, a, b, B, M, N, K, variant=capi.BASIC).reshape(B, 2, M, N)
+    assert np.all(got[:, 0] == 0)
+    assert np.all(got[:, 1] == 2 * K)
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("sw", [64, 128])
+@pytest.mark.parametrize("types", [(ou.F16, ou.F32), (ou.INT1, ou.INT32), (ou.E4M3, ou.F32)],
+                         ids=["f16", "int1", "e4m3"])
+def test_every_tile_configuration(types, sw, bn, monkeypatch):
+    """The tile width (128/256 columns) and stage row width (64/128 bytes) are chosen by a
+    heuristic; force each combination on a multi-tile, multi-k-block, ragged problem."""
+    monkeypatch.setenv("CCGLIB_B200_BN", str(bn))
+    monkeypatch.setenv("CCGLIB_B200_SW", str(sw))
+    type_in, type_out = types
+    B, M, N = 2, 300, 520
+    K = 1056 if type_in == ou.INT1 else 712
+    a, b = make_inputs(22, type_in, B, M, N, K, dist="uniform")
+    for variant in (capi.BASIC, capi.OPT):
+        got = gu.run_gemm(type_in, type_out, a, b, B, M, N, K, variant=variant).reshape(B, 2, M, N)
+        if type_in == ou.INT1:
+            assert np.array_equal(got, gu.oracle_batch(type_in, type_out, a, b, B, M, N, K))
+        else:
+            gu.assert_close_fp64(got, type_in, type_out, a, b, K)
+
+
+def test_interleaved_input_through_transpose():
+    # BASELINE config 2 in miniature: interleaved complex input -> Transpose -> opt GEMM
+    B, M, N, K = 2, 200, 300, 100
+    a, b = make_inputs(23, ou.F16, B, M, N, K, dist="normal", scale=1.0 / np.sqrt(K))
+    a_il = np.ascontiguousarray(a.transpose(0, 2, 3, 1))
+    b_il = np.ascontiguousarray(b.transpose(0, 2, 3, 1))
+    got = gu.run_gemm(ou.F16, ou.F32, a_il, b_il, B, M, N, K, variant=capi.OPT,
+                      in_axis=capi.INTERLEAVED).reshape(B, 2, M, N)
+    gu.assert_close_fp64(got, ou.F16, ou.F32, a, b, K)
+    want = gu.oracle_batch(ou.F16, ou.F32, a, b, B, M, N, K)
+    gu.assert_close_reference_rule(got, want, ou.F16, ou.F32)
+
+
+def test_config1_basic_f16_1024_cubed():
+    # BASELINE config 1 at full size, against the reference's own CPU GEMM where it was built
+    B, M, N, K = 1, 1024, 1024, 1024
+    a, b = make_inputs(1001, ou.F16, B, M, N, K, dist="uniform")
+    got = gu.run_gemm(ou.F16, ou.F32, a, b, B, M, N, K, variant=capi.BASIC).reshape(B, 2, M, N)
+    want = gu.oracle_batch(ou.F16, ou.F32, a, b, B, M, N, K, use_reference=True)
+    gu.assert_close_reference_rule(got, want, ou.F16, ou.F32)
+    ratio = gu.assert_close_fp64(got, ou.F16, ou.F32, a, b, K)
+    print("config1 accumulation error / (sqrt(2K) u S) = %.3f" % ratio)
+
+
+LONG_K = [
+    ("f16-K8192", ou.F16, ou.F32, 2, 256, 512, 8192, "normal"),      # config 2's K
+    ("e4m3-K16384", ou.E4M3, ou.F32, 1, 256, 256, 16384, "fp8"),      # config 4's K
+    ("e5m2-K16384", ou.E5M2, ou.F32, 1, 256, 256, 16384, "fp8"),
+    ("bf16-c5", ou.BF16, ou.F32, 4, 256, 2048, 512, "uniform"),      # config 5's item shape
+    ("tf32-c5", ou.F32, ou.F32, 4, 256, 2048, 512, "uniform"),
+]
+
+
+@pytest.mark.parametrize("case", LONG_K, ids=[c[0] for c in LONG_K])
+def test_baseline_shapes_fp64_gate(case):
+    _, type_in, type_out, B, M, N, K, dist = case
+    if dist == "fp8":
+        # N(0,1) clamped to +-4, scaled to +-0.5 * max finite value, rounded to the fp8 type
+        rng = np.random.default_rng(24)
+        fmax = 448.0 if type_in == ou.E4M3 else 57344.0
+        gen = lambda shape: ou.quantize(
+            (np.clip(rng.standard_normal(shape), -4, 4) / 4 * 0.5 * fmax).astype(np.float32),
+            type_in)
+        a, b = gen((B, 2, M, K)), gen((B, 2, N, K))
+    else:
+        a, b = make_inputs(25, type_in, B, M, N, K, dist=dist,
+                           scale=1.0 / np.sqrt(K) if dist == "normal" else 1.0)
+    got = gu.run_gemm(type_in, type_out, a, b, B, M, N, K, variant=capi.OPT).reshape(B, 2, M, N)
+    ratio = gu.assert_close_fp64(got, type_in, type_out, a, b, K)
+    print("%s accumulation error / (sqrt(2K) u S) = %.3f" % (case[0], ratio))
+
+
+def test_int1_config3_k65536_bit_exact():
+    # BASELINE config 3's K (65536 bits) on one 128 x 256 output tile per batch item
+    B, M, N, K = 2, 128, 256, 65536
+    a, b = make_inputs(26, ou.INT1, B, M, N, K)
+    got = gu.run_gemm(ou.INT1, ou.INT32, a, b, B, M, N, K, variant=capi.OPT).reshape(B, 2, M, N)
+    want = gu.oracle_batch(ou.INT1, ou.INT32, a, b, B, M, N, K)
+    assert np.array_equal(got, want)
+
+
+def test_tf32_ignores_low_mantissa_bits():
+    """float32 input is consumed as tf32: the 13 low mantissa bits are dropped (truncation), which
+    is what the reference assumes (kernels/gemm_kernel_float.cu:80-81) and why its tests mask
+    their inputs (test/gemm/mma.cpp:32-38).  Unmasked input must give the masked result."""
+    B, M, N, K = 1, 128, 128, 64
+    rng = np.random.default_rng(27)
+    a = rng.uniform(-1, 1, (B, 2, M, K)).astype(np.float32)
+    b = rng.uniform(-1, 1, (B, 2, N, K)).astype(np.float32)
+    got = gu.run_gemm(ou.F32, ou.F32, a, b, B, M, N, K, variant=capi.BASIC)
+    got_masked = gu.run_gemm(ou.F32, ou.F32, ou.mask_tf32(a), ou.mask_tf32(b), B, M, N, K,
+                             variant=capi.BASIC)
+    assert np.array_equal(got, got_masked)
+
+
+def test_staged_batch_chunks(monkeypatch):
+    """1-bit input is re-staged through plan-owned scratch in batch chunks; force several chunks."""
+    monkeypatch.setenv("CCGLIB_B200_SCRATCH_MB", "1")
+    B, M, N, K = 5, 128, 256, 1024  # 0.6 MiB of staged bytes per item -> one item per chunk
+    a, b = make_inputs(28, ou.INT1, B, M, N, K)
+    got = gu.run_gemm(ou.INT1, ou.INT32, a, b, B, M, N, K, variant=capi.BASIC).reshape(B, 2, M, N)
+    assert np.array_equal(got, gu.oracle_batch(ou.INT1, ou.INT32, a, b, B, M, N, K))
+
+
+def test_run_twice_same_plan_is_deterministic():
+    import torch
+
+    B, M, N, K = 2, 256, 256, 512
+    a, b = make_inputs(29, ou.F16, B, M, N, K)
+    d_a, d_b = gu.dev(a), gu.dev(b)
+    d_c1 = gu.dev_empty(B * 2 * M * N * 4, 0)
+    d_c2 = gu.dev_empty(B * 2 * M * N * 4, 0)
+    plan = capi.GemmPlan(B, M, N, K, ou.F16, ou.F32, variant=capi.BASIC)
+    plan.run(d_a.data_ptr(), d_b.data_ptr(), d_c1.data_ptr(), gu.stream_handle())
+    plan.run(d_a.data_ptr(), d_b.data_ptr(), d_c2.data_ptr(), gu.stream_handle())
+    torch.cuda.synchronize()
+    gu.check_device_status()
+    assert torch.equal(d_c1, d_c2)
