@@ -12,7 +12,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def test_library_exports_every_declared_symbol():
     header = open(os.path.join(ROOT, "include", "ccglib_b200.h")).read()
-    declared = sorted(set(re.findall(r"CCGLIB_B200_API[^;(]*?\b(ccglib_b200_[a-z_]+)\s*\(", header)))
+    declared = sorted(set(re.findall(r"CCGLIB_B200_API[^;(]*?\b(ccglib_b200_[a-z0-9_]+)\s*\(", header)))
     assert declared == sorted(capi.EXPORTS)
     lib = capi.lib()
     for name in declared:
