@@ -21,6 +21,7 @@ EXPORTS = [
     "ccglib_b200_gemm_plan_destroy", "ccglib_b200_gemm_plan_scratch_bytes",
     "ccglib_b200_transpose_run", "ccglib_b200_pack_run", "ccglib_b200_device_status",
     "ccglib_b200_status_string", "ccglib_b200_last_error",
+    "ccglib_b200_gemm_int1_static_scratch",
 ]
 
 
@@ -67,6 +68,8 @@ def lib() -> ctypes.CDLL:
         L.ccglib_b200_gemm_plan_destroy.restype = ci
         L.ccglib_b200_gemm_plan_scratch_bytes.argtypes = [vp]
         L.ccglib_b200_gemm_plan_scratch_bytes.restype = sz
+        L.ccglib_b200_gemm_int1_static_scratch.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp]
+        L.ccglib_b200_gemm_int1_static_scratch.restype = ci
         L.ccglib_b200_transpose_run.argtypes = [sz, sz, sz, sz, sz, sz, ci, vp, vp, vp]
         L.ccglib_b200_transpose_run.restype = ci
         L.ccglib_b200_pack_run.argtypes = [sz, ci, ci, vp, vp, vp]
@@ -122,6 +125,16 @@ class GemmPlan:
             self.close()
         except Exception:
             pass
+
+
+def gemm_int1_static_scratch(batch, m, n, k, d_a, d_b, d_c, stream: int = 0, variant=BASIC,
+                             c_complex_axis=PLANAR, c_mem_order=ROW_MAJOR, alpha=(1.0, 0.0),
+                             beta=(0.0, 0.0)) -> None:
+    """1-bit GEMM through the entry point that takes its scratch from the library's built-in
+    array instead of allocating (see include/ccglib_b200.h)."""
+    desc = GemmDesc(batch, m, n, k, INT1, INT32, variant, c_complex_axis, ROW_MAJOR, COL_MAJOR,
+                    c_mem_order, alpha[0], alpha[1], beta[0], beta[1])
+    _check(lib().ccglib_b200_gemm_int1_static_scratch(ctypes.byref(desc), d_a, d_b, d_c, stream))
 
 
 def transpose(batch, m, n, m_chunk, n_chunk, nr_bits, input_complex_axis, d_in, d_out,

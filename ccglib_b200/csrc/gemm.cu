@@ -994,3 +994,125 @@ extern "C" int ccglib_b200_device_status(unsigned *word) {
   return value == 0 ? CCGLIB_B200_OK : CCGLIB_B200_DEVICE_TIMEOUT;
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free 1-bit GEMM.
+//
+// Some callers must not allocate device memory at all once they are running: a streaming
+// correlator or beamformer loop whose device memory was handed out in full at start-up (to its own
+// ring buffers or to a framework's caching allocator, so a later cudaMalloc simply fails), and
+// host threads for which the implicit device-wide synchronisation of cudaMalloc / cudaFree would
+// stall every other stream of the process in the middle of an observation.  The 1-bit GEMM needs
+// scratch (the +-1 byte expansion of A and B that the tensor cores read), which a plan normally
+// allocates.  This entry point takes that scratch from a fixed array that is part of the library
+// image instead: every device that loads the library holds kStaticScratchBytes for it until the
+// process exits.
+namespace {
+
+constexpr size_t kStaticScratchBytes = 32u << 20;  // 32 MiB, fixed at build time
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void *g_static_scratch_addr[kMaxDevices] = {nullptr};
+
+// The array's name is only a host-side handle; the address kernels and tensor maps can use comes
+// from cudaGetSymbolAddress, looked up once per device with that device current.
+int static_scratch_address(void **out) {
+  int dev = 0;
+  CCGLIB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    set_last_error("gemm_int1_static_scratch: device ordinal %d out of range", dev);
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void *ptr = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (err != cudaSuccess) return cuda_fail(err, "cudaGetSymbolAddress(g_static_scratch)");
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return CCGLIB_B200_OK;
+}
+
+} // namespace
+
+extern "C" int ccglib_b200_gemm_int1_static_scratch(const ccglib_b200_gemm_desc *desc,
+                                                    const void *d_a, const void *d_b, void *d_c,
+                                                    void *stream) {
+  if (desc == nullptr || d_a == nullptr || d_b == nullptr || d_c == nullptr) {
+    set_last_error("gemm_int1_static_scratch: null argument");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  const ccglib_b200_gemm_desc &d = *desc;
+  if (d.type_in != CCGLIB_B200_INT1 || d.type_out != CCGLIB_B200_INT32) {
+    set_last_error("gemm_int1_static_scratch: only 1-bit input with int32 output is supported");
+    return CCGLIB_B200_UNSUPPORTED;
+  }
+  if (d.batch == 0 || d.m == 0 || d.n == 0 || d.k == 0 || d.m > 0x7FFFFFFFull ||
+      d.n > 0x7FFFFFFFull || d.k > 0x7FFFFFFFull || d.batch > 0x3FFFFFFFull) {
+    set_last_error("gemm_int1_static_scratch: batch, M, N and K must be positive and below 2^31");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  if (d.variant != CCGLIB_B200_BASIC && d.variant != CCGLIB_B200_OPT) {
+    set_last_error("gemm_int1_static_scratch: unknown variant %d", d.variant);
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  if (d.variant == CCGLIB_B200_BASIC && d.c_complex_axis == CCGLIB_B200_INTERLEAVED) {
+    set_last_error("complex-interleaved output is not supported in basic variant");
+    return CCGLIB_B200_UNSUPPORTED;
+  }
+  if (d.a_mem_order != CCGLIB_B200_ROW_MAJOR || d.b_mem_order != CCGLIB_B200_COL_MAJOR) {
+    set_last_error("GEMM needs row-major A and col-major B");
+    return CCGLIB_B200_UNSUPPORTED;
+  }
+  // A plan-shaped description on the stack; nothing here allocates on the host or the device.
+  ccglib_b200_gemm_plan plan{};
+  plan.desc = d;
+  plan.a_planes = 3;
+  plan.stage_mode = kExpandBits;
+  plan.k_bytes = d.k;
+  plan.pitch = ceil_div<size_t>(d.k, 16) * 16;
+  plan.out_elem_bytes = 4;
+  const size_t per_item_a = 3 * d.m * plan.pitch;
+  const size_t per_item_b = 2 * d.n * plan.pitch;
+  if (per_item_a + per_item_b > kStaticScratchBytes) {
+    set_last_error("gemm_int1_static_scratch: one batch item needs (3*M + 2*N) * K = %zu bytes of "
+                   "scratch but the built-in array holds %zu; use a plan (gemm_plan_create) for "
+                   "this size",
+                   per_item_a + per_item_b, kStaticScratchBytes);
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  CCGLIB_CUDA_TRY(cudaGetDevice(&plan.device));
+  plan.sms = sm_count();
+  if (plan.sms <= 0) return CCGLIB_B200_CUDA_ERROR;
+  int cc_major = 0;
+  CCGLIB_CUDA_TRY(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, plan.device));
+  if (cc_major != 10) {
+    set_last_error("This architecture is not supported (need compute capability 10.x)");
+    return CCGLIB_B200_UNSUPPORTED;
+  }
+  const size_t tiles_256 = d.batch * ceil_div<size_t>(d.m, kBlockM) * ceil_div<size_t>(d.n, 256);
+  plan.bn = (plan.k_bytes <= 2048 || tiles_256 < static_cast<size_t>(plan.sms)) ? 128 : 256;
+  plan.sw = 64;
+  plan.kernel = pick_tile<kKindI8, 3, int>(plan.bn, plan.sw);
+  plan.idesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(plan.bn >> 3) << 17) |
+               (static_cast<uint32_t>(kBlockM >> 4) << 24);  // s32 accumulate, signed 8-bit A and B
+  plan.idesc_neg_a = plan.idesc;
+  CCGLIB_CUDA_TRY(cudaFuncSetAttribute(reinterpret_cast<const void *>(plan.kernel.fn),
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       plan.kernel.smem));
+  void *scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != CCGLIB_B200_OK) return rc;
+  size_t chunk = kStaticScratchBytes / (per_item_a + per_item_b);
+  if (chunk > d.batch) chunk = d.batch;
+  plan.batch_chunk = chunk;
+  plan.scratch_bytes = 0;  // nothing owned
+  plan.scratch_a = scratch;
+  plan.scratch_b = static_cast<char *>(scratch) + chunk * per_item_a;
+  // Every byte the multiply reads from the array is rewritten by this call's own expansion pass
+  // (rows are written in full, zero padding included), so nothing has to start at zero and
+  // whatever an earlier call left behind is never read.
+  return ccglib_b200_gemm_run(&plan, d_a, d_b, d_c, stream);
+}

@@ -130,6 +130,28 @@ CCGLIB_B200_API int ccglib_b200_transpose_run(size_t batch, size_t m, size_t n, 
 CCGLIB_B200_API int ccglib_b200_pack_run(size_t n, int direction, int input_complex_axis, const void *d_in,
                          void *d_out, void *stream);
 
+/*
+ * 1-bit complex GEMM that allocates nothing, for callers that cannot call cudaMalloc: a
+ * correlator or beamformer loop whose device memory was handed out in full at start-up (a later
+ * allocation would fail), or a host thread that cannot afford the device-wide synchronisation an
+ * allocation or free implies while other streams are in the middle of an observation.  It has no
+ * counterpart in the reference, whose GEMM needs no scratch.  Same arithmetic, layouts and
+ * errors as a plan created from `desc` and run once (type_in must be INT1, type_out INT32), but
+ * the scratch for the +-1 byte expansion of A and B is a fixed 32 MiB array inside the library
+ * image (each GPU that loads the library holds it until the process exits) instead of a plan
+ * allocation.
+ *   - Limit: one batch item must fit, (3*M + 2*N) * round_up(K, 16) <= 32 MiB; larger problems
+ *     get INVALID_ARGUMENT and should use a plan.  Batches are processed in chunks that fit.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current); make that first call before starting any stream capture on that device.
+ *   - All calls on a device share the one array and it keeps the last call's contents.  Nothing
+ *     has to be cleared: each call rewrites every row it later reads, padding included.  Calls
+ *     that can overlap on the GPU (different streams, or threads) race on it; serialise them.
+ */
+CCGLIB_B200_API int ccglib_b200_gemm_int1_static_scratch(const ccglib_b200_gemm_desc *desc,
+                                                         const void *d_a, const void *d_b,
+                                                         void *d_c, void *stream);
+
 /* Read and clear the sticky device-side status word of the current device (synchronises the
  * device).  Non-zero means a bounded wait inside a kernel gave up; its results are invalid. */
 CCGLIB_B200_API int ccglib_b200_device_status(unsigned *word);
