@@ -50,6 +50,11 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "c2_f16_opt_8192_b64"
 
+# DRAM bytes (read + write) of one GEMM launch per batch item, from the ncu capture summarised in
+# profiles/cgemm_tcgen05_f16_opt_8192_batch2_ncu_full.md (5.96 GB for 2 items; items are walked
+# one after another, so traffic grows in proportion to the batch).
+NCU_DRAM_BYTES_PER_ITEM = {"c2_f16_opt_8192_b64": 2.98e9}
+
 
 def measured_peaks() -> dict:
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -531,6 +536,7 @@ def run_ours(args, name):
     ms_step = float(t[0]) / args.steps
     gemm_ms_max = float(t[1])
     check = wl.spot_check()
+    wl_bits = wl.bits
     hbm_gb = wl.hbm_bytes() / 1e9
     launches = wl.launches_per_step * args.steps
     total_flops = 8.0 * M * N * K * B_total
@@ -564,7 +570,10 @@ def run_ours(args, name):
         achieved = gemm_flops_rank / (gemm_ms_max * 1e-3) / 1e12
         roofline = {
             "bound": "tensor", "kernel": "cgemm_tcgen05_kernel", "achieved": achieved,
-            "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+            "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+            "traffic": (NCU_DRAM_BYTES_PER_ITEM[name] * share[0]
+                        if name in NCU_DRAM_BYTES_PER_ITEM else None),
+            "algorithmic_bytes": share[0] * (2.0 * (M + N) * K * wl_bits / 8 + 2.0 * M * N * 4),
             "peak_source": "%s sustained bf16 GEMM x %.2g (dtype rate ratio)" % (
                 peaks["source"], scale),
             "frac_of_burst": achieved / (peaks["bf16_tflops"] * scale),
