@@ -772,7 +772,7 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
   // so the epilogue overlaps the next tile's main loop (short K) and gives more tiles (small M*N).
   const size_t tiles_256 = d.batch * ceil_div<size_t>(d.m, kBlockM) * ceil_div<size_t>(d.n, 256);
   int bn = (plan.k_bytes <= 2048 || tiles_256 < static_cast<size_t>(plan.sms)) ? 128 : 256;
-  int sw = 64;
+  int sw = 128;
   bn = env_int("CCGLIB_B200_BN", bn);
   sw = env_int("CCGLIB_B200_SW", sw);
   if ((bn != 128 && bn != 256) || (sw != 64 && sw != 128)) {
@@ -1094,7 +1094,7 @@ extern "C" int ccglib_b200_gemm_int1_static_scratch(const ccglib_b200_gemm_desc 
   }
   const size_t tiles_256 = d.batch * ceil_div<size_t>(d.m, kBlockM) * ceil_div<size_t>(d.n, 256);
   plan.bn = (plan.k_bytes <= 2048 || tiles_256 < static_cast<size_t>(plan.sms)) ? 128 : 256;
-  plan.sw = 64;
+  plan.sw = 128;
   plan.kernel = pick_tile<kKindI8, 3, int>(plan.bn, plan.sw);
   plan.idesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(plan.bn >> 3) << 17) |
                (static_cast<uint32_t>(kBlockM >> 4) << 24);  // s32 accumulate, signed 8-bit A and B
