@@ -492,7 +492,9 @@ def run_ours(args, name):
     if args.batch:
         B_total = args.batch
     # batch items are independent GEMMs: rank r takes a contiguous share, no collective needed
-    share = [B_total // world + (1 if r < B_total % world else 0) for r in range(world)]
+    from ccglib_b200 import sharding
+
+    share = sharding.batch_shares(B_total, world)
     B = share[rank]
     if B == 0:
         raise SystemExit("batch %d cannot be split over %d ranks" % (B_total, world))

@@ -63,21 +63,25 @@ struct GemmParams {
   void *c;
   uint32_t c_layout;
   uint32_t have_alpha, have_beta, vec_ok;
+  uint32_t epi_tma;  // stage C through shared memory and store it with TMA (row-major planar)
   float alpha_re, alpha_im, beta_re, beta_im;
   unsigned int *status;
 };
 
-template <int BN, int SW, int A_PLANES> struct Cfg {
+constexpr int kStagingBytes = 4 * 2 * 32 * 128;  // per epilogue warp: (re, im) x 32 rows x 128 B
+
+template <int BN, int SW, int A_PLANES, bool EPI_TMA> struct Cfg {
   static constexpr int kAPlane = kBlockM * SW;
   static constexpr int kBPlane = BN * SW;
   static constexpr int kABytes = A_PLANES * kAPlane;
   static constexpr int kBBytes = 2 * kBPlane;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kStagesRaw = (kMaxSmem - 1024 - kBarrierBytes) / kStageBytes;
+  static constexpr int kStaging = EPI_TMA ? kStagingBytes : 0;
+  static constexpr int kStagesRaw = (kMaxSmem - 1024 - kBarrierBytes - kStaging) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kAccStages = (BN == 128) ? 2 : 1;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kBarrierBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStaging + 1024 + kBarrierBytes;
   static_assert(kStages >= 2, "need at least two stages");
   static_assert(2 * BN * kAccStages <= kTmemCols, "accumulators exceed tensor memory");
 };
@@ -202,18 +206,50 @@ __device__ __forceinline__ void store_run(OutT *dst, const Acc (&v)[COUNT], int 
   }
 }
 
-// Epilogue for one row (m) and 32 consecutive columns starting at n0 of batch item b.
+// Element offsets of C for (row m, column n0) of batch item b in the requested layout.
+struct COffsets {
+  size_t base_re, stride_j, off_im;
+};
+
+__device__ __forceinline__ COffsets c_offsets(const GemmParams &p, uint32_t b, uint32_t m,
+                                              uint32_t n0) {
+  const size_t M = p.M, N = p.N;
+  COffsets o;
+  switch (p.c_layout) {
+  case kPlanarRow:
+    o.base_re = ((size_t)b * 2 * M + m) * N + n0;
+    o.stride_j = 1;
+    o.off_im = M * N;
+    break;
+  case kPlanarCol:
+    o.base_re = ((size_t)b * 2 * N + n0) * M + m;
+    o.stride_j = M;
+    o.off_im = M * N;
+    break;
+  case kInterRow:
+    o.base_re = (((size_t)b * M + m) * N + n0) * 2;
+    o.stride_j = 2;
+    o.off_im = 1;
+    break;
+  default:
+    o.base_re = (((size_t)b * N + n0) * M + m) * 2;
+    o.stride_j = 2 * M;
+    o.off_im = 1;
+    break;
+  }
+  return o;
+}
+
+// Accumulator bits -> values with alpha and beta applied (row m, 32 columns from n0).
 template <typename OutT>
-__device__ __forceinline__ void epilogue_chunk(const GemmParams &p, uint32_t b, uint32_t m,
-                                               uint32_t n0, const uint32_t (&bits_re)[32],
-                                               const uint32_t (&bits_im)[32]) {
+__device__ __forceinline__ void epilogue_values(const GemmParams &p, const COffsets &o, bool row_ok,
+                                                int valid, const uint32_t (&bits_re)[32],
+                                                const uint32_t (&bits_im)[32],
+                                                typename OutTraits<OutT>::Acc (&re)[32],
+                                                typename OutTraits<OutT>::Acc (&im)[32]) {
   using Tr = OutTraits<OutT>;
   using Acc = typename Tr::Acc;
-  if (m >= p.M) return;
-  OutT *C = static_cast<OutT *>(p.c);
-  const size_t M = p.M, N = p.N;
-  const int valid = static_cast<int>(min(32u, p.N - n0));
-  Acc re[32], im[32];
+  const OutT *C = static_cast<const OutT *>(p.c);
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
     re[j] = Tr::from_bits(bits_re[j]);
@@ -228,45 +264,37 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, uint32_t b, 
       im[j] = ai * r + ar * im[j];
     }
   }
-  // element offsets of (re, im) for column j
-  size_t base_re, stride_j, off_im;
-  switch (p.c_layout) {
-  case kPlanarRow:
-    base_re = ((size_t)b * 2 * M + m) * N + n0;
-    stride_j = 1;
-    off_im = M * N;
-    break;
-  case kPlanarCol:
-    base_re = ((size_t)b * 2 * N + n0) * M + m;
-    stride_j = M;
-    off_im = M * N;
-    break;
-  case kInterRow:
-    base_re = (((size_t)b * M + m) * N + n0) * 2;
-    stride_j = 2;
-    off_im = 1;
-    break;
-  default:
-    base_re = (((size_t)b * N + n0) * M + m) * 2;
-    stride_j = 2 * M;
-    off_im = 1;
-    break;
-  }
-  if (p.have_beta) {
+  if (p.have_beta && row_ok) {
     const Acc br = static_cast<Acc>(p.beta_re), bi = static_cast<Acc>(p.beta_im);
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       if (j < valid) {
-        const Acc cr = Tr::to_acc(C[base_re + j * stride_j]);
-        const Acc ci = Tr::to_acc(C[base_re + j * stride_j + off_im]);
+        const Acc cr = Tr::to_acc(C[o.base_re + j * o.stride_j]);
+        const Acc ci = Tr::to_acc(C[o.base_re + j * o.stride_j + o.off_im]);
         re[j] += br * cr - bi * ci;
         im[j] += bi * cr + br * ci;
       }
     }
   }
+}
+
+// Epilogue for one row (m) and 32 consecutive columns starting at n0 of batch item b, stored
+// straight from registers.
+template <typename OutT>
+__device__ __forceinline__ void epilogue_chunk(const GemmParams &p, uint32_t b, uint32_t m,
+                                               uint32_t n0, const uint32_t (&bits_re)[32],
+                                               const uint32_t (&bits_im)[32]) {
+  using Tr = OutTraits<OutT>;
+  using Acc = typename Tr::Acc;
+  if (m >= p.M) return;
+  OutT *C = static_cast<OutT *>(p.c);
+  const int valid = static_cast<int>(min(32u, p.N - n0));
+  const COffsets o = c_offsets(p, b, m, n0);
+  Acc re[32], im[32];
+  epilogue_values<OutT>(p, o, true, valid, bits_re, bits_im, re, im);
   if (p.c_layout == kPlanarRow) {
-    store_run<OutT, 32>(C + base_re, re, valid, p.vec_ok != 0);
-    store_run<OutT, 32>(C + base_re + off_im, im, valid, p.vec_ok != 0);
+    store_run<OutT, 32>(C + o.base_re, re, valid, p.vec_ok != 0);
+    store_run<OutT, 32>(C + o.base_re + o.off_im, im, valid, p.vec_ok != 0);
   } else if (p.c_layout == kInterRow) {
     Acc both[64];
 #pragma unroll
@@ -274,24 +302,73 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, uint32_t b, 
       both[2 * j] = re[j];
       both[2 * j + 1] = im[j];
     }
-    store_run<OutT, 64>(C + base_re, both, 2 * valid, p.vec_ok != 0);
+    store_run<OutT, 64>(C + o.base_re, both, 2 * valid, p.vec_ok != 0);
   } else {
     // column-major: consecutive lanes hold consecutive m, so each store is coalesced as is
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       if (j < valid) {
-        C[base_re + j * stride_j] = Tr::to_out(re[j]);
-        C[base_re + j * stride_j + off_im] = Tr::to_out(im[j]);
+        C[o.base_re + j * o.stride_j] = Tr::to_out(re[j]);
+        C[o.base_re + j * o.stride_j + o.off_im] = Tr::to_out(im[j]);
       }
     }
   }
 }
 
-template <int KIND, int BN, int SW, int A_PLANES, typename OutT>
+// One warp writes its 32 rows x 32 four-byte columns into a 4 KiB staging tile laid out the way a
+// 128-byte-swizzled TMA store reads it (16-byte chunk j of row r sits at chunk j ^ (r & 7)), then
+// lane 0 issues the store.  The tile is reused only after the previous store from it has finished
+// reading (at most one younger store, from the other plane's tile, may still be pending).
+template <typename Acc>
+__device__ __forceinline__ void staged_store(const CUtensorMap *tm_c, uint32_t tile, uint32_t lane,
+                                             const Acc (&v)[32], bool issue, int32_t x, int32_t y,
+                                             int32_t z) {
+  if (lane == 0) bulk_wait_group_read<1>();
+  __syncwarp();
+  const uint32_t row = tile + lane * 128;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    st_shared_v4(row + ((j ^ (lane & 7)) << 4), Packer<Acc>::word(&v[4 * j]),
+                 Packer<Acc>::word(&v[4 * j + 1]), Packer<Acc>::word(&v[4 * j + 2]),
+                 Packer<Acc>::word(&v[4 * j + 3]));
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0 && issue) {
+    tma_store_3d(tm_c, tile, x, y, z);
+    bulk_commit_group();
+  }
+}
+
+// Epilogue for 32 rows (one per lane, first row m0) and 32 columns from n0, stored through the
+// warp's staging tiles with TMA (row-major planar C with four-byte elements).
+template <typename OutT>
+__device__ __forceinline__ void epilogue_chunk_staged(const GemmParams &p, const CUtensorMap *tm_c,
+                                                      uint32_t staging, uint32_t lane, uint32_t b,
+                                                      uint32_t m0, uint32_t n0,
+                                                      const uint32_t (&bits_re)[32],
+                                                      const uint32_t (&bits_im)[32]) {
+  using Acc = typename OutTraits<OutT>::Acc;
+  static_assert(sizeof(OutT) == 4, "staged epilogue is for four-byte outputs");
+  const uint32_t m = m0 + lane;
+  const int valid = static_cast<int>(min(32u, p.N - n0));
+  const COffsets o = c_offsets(p, b, m, n0);
+  Acc re[32], im[32];
+  epilogue_values<OutT>(p, o, m < p.M, valid, bits_re, bits_im, re, im);
+  const bool issue = m0 < p.M;
+  const int32_t x = static_cast<int32_t>(n0 * 4);  // the tensor map is byte-typed
+  staged_store<Acc>(tm_c, staging, lane, re, issue, x, static_cast<int32_t>(m0),
+                    static_cast<int32_t>(2 * b));
+  staged_store<Acc>(tm_c, staging + 4096, lane, im, issue, x, static_cast<int32_t>(m0),
+                    static_cast<int32_t>(2 * b + 1));
+}
+
+template <int KIND, int BN, int SW, int A_PLANES, typename OutT, bool EPI_TMA>
 __global__ void __launch_bounds__(kThreads, 1)
 cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
-                     const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
-  using C = Cfg<BN, SW, A_PLANES>;
+                     const __grid_constant__ CUtensorMap tm_b,
+                     const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
+  using C = Cfg<BN, SW, A_PLANES, EPI_TMA>;
   constexpr int kStages = C::kStages;
   constexpr int kAccStages = C::kAccStages;
   constexpr int kSub = SW / 32;  // 32-byte MMA k-steps per stage
@@ -299,7 +376,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~static_cast<uintptr_t>(1023u));
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * C::kStageBytes);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * C::kStageBytes + C::kStaging);
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * kStages;
   const uint32_t bar_acc_full = bar_empty + 8 * kStages;
@@ -324,6 +401,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     fence_mbar_init();
     prefetch_tensormap(&tm_a);
     prefetch_tensormap(&tm_b);
+    if (EPI_TMA && p.epi_tma) prefetch_tensormap(&tm_c);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
@@ -469,6 +547,14 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         tmem_ld_32x32b_x32(t_re + c0, bits_re);
         tmem_ld_32x32b_x32(t_re + BN + c0, bits_im);
         tmem_wait_ld();
+        if constexpr (EPI_TMA) {
+          if (p.epi_tma) {
+            const uint32_t staging = smem_base + kStages * C::kStageBytes + quad * 8192;
+            epilogue_chunk_staged<OutT>(p, &tm_c, staging, lane, t.b,
+                                        t.mt * kBlockM + quad * 32, n0, bits_re, bits_im);
+            continue;
+          }
+        }
         epilogue_chunk<OutT>(p, t.b, m, n0, bits_re, bits_im);
       }
       tc_fence_before();
@@ -477,6 +563,11 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         acc = 0;
         acc_phase ^= 1;
       }
+    }
+    if constexpr (EPI_TMA) {
+      // the staging tiles must outlive the stores that read them
+      if (p.epi_tma && lane == 0) bulk_wait_group<0>();
+      __syncwarp();
     }
   }
 
@@ -540,15 +631,21 @@ int make_map(CUtensorMap *tm, const void *base, uint64_t row_bytes, uint64_t row
   return CCGLIB_B200_OK;
 }
 
-using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const GemmParams);
+using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                          const GemmParams);
 
 struct KernelEntry {
   KernelFn fn;
   int smem;
+  bool epi_tma;  // the instance reserves staging tiles for the TMA-store epilogue
 };
 
+// Four-byte outputs get the TMA-store epilogue wherever its 32 KiB of staging costs no pipeline
+// stage; that is everywhere except three A planes with 256-column tiles.
 template <int KIND, int BN, int SW, int A_PLANES, typename OutT> KernelEntry entry() {
-  return {cgemm_tcgen05_kernel<KIND, BN, SW, A_PLANES, OutT>, Cfg<BN, SW, A_PLANES>::kSmemBytes};
+  constexpr bool kEpiTma = sizeof(OutT) == 4 && !(A_PLANES == 3 && BN == 256);
+  return {cgemm_tcgen05_kernel<KIND, BN, SW, A_PLANES, OutT, kEpiTma>,
+          Cfg<BN, SW, A_PLANES, kEpiTma>::kSmemBytes, kEpiTma};
 }
 
 template <int KIND, int A_PLANES, typename OutT> KernelEntry pick_tile(int bn, int sw) {
@@ -909,12 +1006,19 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
   // 16-byte stores need every row run to start on a 16-byte boundary
   const size_t run_bytes = (planar ? d.n : 2 * d.n) * plan.out_elem_bytes;
   p.vec_ok = (row && aligned16(c) && run_bytes % 16 == 0) ? 1u : 0u;
+  // TMA-store epilogue: row-major planar C with four-byte elements, 16-byte aligned rows
+  CUtensorMap tm_c = tm_a;  // placeholder when the epilogue stores straight from registers
+  p.epi_tma = (plan.kernel.epi_tma && planar && p.vec_ok && plan.out_elem_bytes == 4) ? 1u : 0u;
+  if (p.epi_tma) {
+    rc = make_map(&tm_c, c, d.n * 4, d.m, 2 * nb, d.n * 4, d.m * d.n * 4, 128, 32, 1);
+    if (rc != CCGLIB_B200_OK) return rc;
+  }
   if (cudaGetSymbolAddress(reinterpret_cast<void **>(&p.status), g_device_status) != cudaSuccess) {
     return cuda_fail(cudaGetLastError(), "cudaGetSymbolAddress(g_device_status)");
   }
   const unsigned grid = static_cast<unsigned>(tiles < static_cast<size_t>(plan.sms) ? tiles
                                                                                    : plan.sms);
-  plan.kernel.fn<<<grid, kThreads, plan.kernel.smem, stream>>>(tm_a, tm_b, p);
+  plan.kernel.fn<<<grid, kThreads, plan.kernel.smem, stream>>>(tm_a, tm_b, tm_c, p);
   CCGLIB_CUDA_TRY(cudaGetLastError());
   return CCGLIB_B200_OK;
 }
