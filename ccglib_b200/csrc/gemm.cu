@@ -580,6 +580,265 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   }
 }
 
+// ------------------------------------------------------------------------------ CTA pairs
+//
+// Same computation with the two SMs of a TPC working as one: a cluster of two CTAs shares one
+// 256 x BN tile.  Each CTA stages its own 128 rows of A and only half of the B tile (BN/2 rows);
+// one thread of the leader CTA (cluster rank 0) issues tcgen05.mma.cta_group::2 with M = 256, which
+// makes each SM multiply its A rows by the whole B tile, reading the other half from the peer's
+// shared memory.  Per flop this halves the B bytes fetched from L2 and cuts the operand bytes
+// read from shared memory by a third, which is what the clock under the power cap and the L2
+// bandwidth of short-K problems are limited by.
+//
+// Hand-over: both producers arm and fill the LEADER's full barrier (2 arrivals + both CTAs' bytes;
+// loads carry .cta_group::2 so that they may signal the peer's barrier, never multicast); the
+// leader's commits arrive on each CTA's own empty / acc_full barriers; all 256 epilogue threads
+// of the pair arrive on the leader's acc_empty barrier.  Set-up and tear-down are cluster-wide
+// barriers, so neither CTA leaves while the other may still touch its shared memory.
+
+template <int BN, int A_PLANES, bool EPI_TMA> struct PairCfg {
+  static constexpr int kSw = 128;
+  static constexpr int kAPlane = kBlockM * kSw;
+  static constexpr int kBPlane = (BN / 2) * kSw;
+  static constexpr int kABytes = A_PLANES * kAPlane;
+  static constexpr int kBBytes = 2 * kBPlane;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kStaging = EPI_TMA ? kStagingBytes : 0;
+  static constexpr int kStagesRaw = (kMaxSmem - 1024 - kBarrierBytes - kStaging) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kAccStages = (BN == 128) ? 2 : 1;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStaging + 1024 + kBarrierBytes;
+  static_assert(kStages >= 2, "need at least two stages");
+};
+
+template <int KIND, int BN, int A_PLANES, typename OutT, bool EPI_TMA>
+__global__ void __launch_bounds__(kThreads, 1)
+cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
+                  const __grid_constant__ CUtensorMap tm_b,
+                  const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
+  using C = PairCfg<BN, A_PLANES, EPI_TMA>;
+  constexpr int kStages = C::kStages;
+  constexpr int kAccStages = C::kAccStages;
+  constexpr int SW = C::kSw;
+  constexpr int kSub = SW / 32;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~static_cast<uintptr_t>(1023u));
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * C::kStageBytes + C::kStaging);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * kStages;
+  const uint32_t bar_acc_full = bar_empty + 8 * kStages;
+  const uint32_t bar_acc_empty = bar_acc_full + 8 * kAccStages;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 2 * kAccStages);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  const uint32_t smem_base = smem_u32(smem);
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const uint32_t pair = cluster_id_x();
+  const uint32_t num_pairs = cluster_count_x();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 2);  // one arrival per producer of the pair (used in the leader)
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < kAccStages; ++s) {
+      mbar_init(bar_acc_full + 8 * s, 1);
+      mbar_init(bar_acc_empty + 8 * s, 256);  // epilogue threads of both CTAs (used in the leader)
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_b);
+    if (EPI_TMA && p.epi_tma) prefetch_tensormap(&tm_c);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync();  // the peer's barriers must be initialised before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    uint32_t stage = 0, phase = 0;
+    uint32_t issued = 0;
+    bool ok = true;
+    for (uint32_t tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
+      const TileCoord t = decode_tile(p, tile);
+      const uint32_t mt = t.mt * 2 + rank;  // this CTA's 128-row block
+      for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+        if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status,
+                       kDevTimeoutProducer)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          int32_t ax, ay, az, bx, by, bz;
+          const uint32_t n_glob = t.nt * BN + rank * (BN / 2);
+          if (p.tiled) {
+            const uint32_t slab = kb / p.k_per_slab;
+            ax = bx = static_cast<int32_t>((kb - slab * p.k_per_slab) * SW);
+            // a row block past the last slab reads nothing this CTA will store; keep it in range
+            const uint32_t mt_slab = min(mt, p.a_slabs_m - 1);
+            ay = 0;
+            az = static_cast<int32_t>(2 * ((t.b * p.a_slabs_m + mt_slab) * p.slabs_k + slab));
+            const uint32_t slab_n = min(n_glob / p.b_slab_rows, p.b_slabs_n - 1);
+            by = static_cast<int32_t>(n_glob - (n_glob / p.b_slab_rows) * p.b_slab_rows);
+            bz = static_cast<int32_t>(2 * ((t.b * p.b_slabs_n + slab_n) * p.slabs_k + slab));
+          } else {
+            ax = bx = static_cast<int32_t>(kb * SW);
+            ay = static_cast<int32_t>(mt * kBlockM);
+            az = static_cast<int32_t>(t.b * A_PLANES);
+            by = static_cast<int32_t>(n_glob);
+            bz = static_cast<int32_t>(t.b * 2);
+          }
+          const uint32_t full = map_to_cta(bar_full + 8 * stage, 0);
+          const uint32_t dst = smem_base + stage * C::kStageBytes;
+          mbar_arrive_expect_tx_cluster(full, C::kStageBytes);
+          tma_load_3d_pair(dst, &tm_a, ax, ay, az, full);
+          tma_load_3d_pair(dst + C::kABytes, &tm_b, bx, by, bz, full);
+        }
+        __syncwarp();
+        issued |= 1u << stage;
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    if (*abort_flag && rank == 0) {
+      // The leader's full barriers count the bytes of both CTAs: wait (bounded) for the last
+      // load of every stage before the pair meets at the closing cluster barrier.
+      for (int s = 0; s < kStages; ++s) {
+        if (!(issued & (1u << s))) continue;
+        const uint32_t last_parity = (static_cast<uint32_t>(s) < stage) ? phase : (phase ^ 1);
+        const long long t0 = clock64();
+        while (!mbar_try_wait(bar_full + 8 * s, last_parity)) {
+          if (clock64() - t0 > kWaitLimitCycles) {
+            atomicOr(p.status, kDevTimeoutDrain);
+            break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (rank == 0) {
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (uint32_t tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
+        if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1, abort_flag, p.status,
+                       kDevTimeoutMma)) {
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_re = tmem_base + acc * (2 * BN);
+        const uint32_t d_im = d_re + BN;
+        for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kDevTimeoutMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t a_base = smem_base + stage * C::kStageBytes;
+            const uint32_t b_base = a_base + C::kABytes;
+#pragma unroll
+            for (int k = 0; k < kSub; ++k) {
+              const uint64_t a_re = smem_desc<SW>(a_base + k * 32);
+              const uint64_t a_im = smem_desc<SW>(a_base + C::kAPlane + k * 32);
+              const uint64_t b_re = smem_desc<SW>(b_base + k * 32);
+              const uint64_t b_im = smem_desc<SW>(b_base + C::kBPlane + k * 32);
+              const uint32_t accum = (kb | static_cast<uint32_t>(k)) != 0 ? 1u : 0u;
+              tc_mma_pair<KIND>(d_re, a_re, b_re, p.idesc, accum);
+              tc_mma_pair<KIND>(d_im, a_re, b_im, p.idesc, accum);
+              tc_mma_pair<KIND>(d_im, a_im, b_re, p.idesc, 1u);
+              if constexpr (A_PLANES == 3) {
+                const uint64_t a_neg = smem_desc<SW>(a_base + 2 * C::kAPlane + k * 32);
+                tc_mma_pair<KIND>(d_re, a_neg, b_im, p.idesc, 1u);
+              } else {
+                tc_mma_pair<KIND>(d_re, a_im, b_im, p.idesc_neg_a, 1u);
+              }
+            }
+            // the stage is free in both CTAs once these MMAs have read it
+            tc_commit_pair(map_to_cta(bar_empty + 8 * stage, 0));
+            tc_commit_pair(map_to_cta(bar_empty + 8 * stage, 1));
+            if (kb + 1 == p.k_blocks) {
+              tc_commit_pair(map_to_cta(bar_acc_full + 8 * acc, 0));
+              tc_commit_pair(map_to_cta(bar_acc_full + 8 * acc, 1));
+            }
+          }
+          __syncwarp();
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (++acc == kAccStages) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps (both CTAs)
+    const uint32_t quad = warp & 3;
+    uint32_t acc = 0, acc_phase = 0;
+    for (uint32_t tile = pair; tile < p.num_tiles; tile += num_pairs) {
+      const TileCoord t = decode_tile(p, tile);
+      if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, p.status,
+                     kDevTimeoutEpilogue)) {
+        break;
+      }
+      tc_fence_after();
+      const uint32_t m0 = (t.mt * 2 + rank) * kBlockM + quad * 32;
+      const uint32_t t_re = tmem_base + ((quad * 32) << 16) + acc * (2 * BN);
+#pragma unroll 1
+      for (uint32_t c0 = 0; c0 < BN; c0 += 32) {
+        const uint32_t n0 = t.nt * BN + c0;
+        if (n0 >= p.N) break;
+        uint32_t bits_re[32], bits_im[32];
+        tmem_ld_32x32b_x32(t_re + c0, bits_re);
+        tmem_ld_32x32b_x32(t_re + BN + c0, bits_im);
+        tmem_wait_ld();
+        if constexpr (EPI_TMA) {
+          if (p.epi_tma) {
+            const uint32_t staging = smem_base + kStages * C::kStageBytes + quad * 8192;
+            epilogue_chunk_staged<OutT>(p, &tm_c, staging, lane, t.b, m0, n0, bits_re, bits_im);
+            continue;
+          }
+        }
+        epilogue_chunk<OutT>(p, t.b, m0 + lane, n0, bits_re, bits_im);
+      }
+      tc_fence_before();
+      mbar_arrive_cluster(map_to_cta(bar_acc_empty + 8 * acc, 0));
+      if (++acc == kAccStages) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+    if constexpr (EPI_TMA) {
+      if (p.epi_tma && lane == 0) bulk_wait_group<0>();
+      __syncwarp();
+    }
+  }
+
+  // ------------------------------------------------------------------ tear-down
+  tc_fence_before();
+  cluster_sync();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
 // ------------------------------------------------------------------------------ host side
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -638,6 +897,7 @@ struct KernelEntry {
   KernelFn fn;
   int smem;
   bool epi_tma;  // the instance reserves staging tiles for the TMA-store epilogue
+  bool pair;     // CTA-pair kernel: launched as clusters of two, tiles are 256 rows high
 };
 
 // Four-byte outputs get the TMA-store epilogue wherever its 32 KiB of staging costs no pipeline
@@ -645,10 +905,21 @@ struct KernelEntry {
 template <int KIND, int BN, int SW, int A_PLANES, typename OutT> KernelEntry entry() {
   constexpr bool kEpiTma = sizeof(OutT) == 4 && !(A_PLANES == 3 && BN == 256);
   return {cgemm_tcgen05_kernel<KIND, BN, SW, A_PLANES, OutT, kEpiTma>,
-          Cfg<BN, SW, A_PLANES, kEpiTma>::kSmemBytes, kEpiTma};
+          Cfg<BN, SW, A_PLANES, kEpiTma>::kSmemBytes, kEpiTma, false};
 }
 
-template <int KIND, int A_PLANES, typename OutT> KernelEntry pick_tile(int bn, int sw) {
+template <int KIND, int BN, int A_PLANES, typename OutT> KernelEntry pair_entry() {
+  constexpr bool kEpiTma = sizeof(OutT) == 4;
+  return {cgemm_pair_kernel<KIND, BN, A_PLANES, OutT, kEpiTma>,
+          PairCfg<BN, A_PLANES, kEpiTma>::kSmemBytes, kEpiTma, true};
+}
+
+template <int KIND, int A_PLANES, typename OutT>
+KernelEntry pick_tile(int bn, int sw, bool pair = false) {
+  if (pair) {
+    return bn == 256 ? pair_entry<KIND, 256, A_PLANES, OutT>()
+                     : pair_entry<KIND, 128, A_PLANES, OutT>();
+  }
   if (bn == 256) {
     return sw == 128 ? entry<KIND, 256, 128, A_PLANES, OutT>()
                      : entry<KIND, 256, 64, A_PLANES, OutT>();
@@ -657,16 +928,16 @@ template <int KIND, int A_PLANES, typename OutT> KernelEntry pick_tile(int bn, i
                    : entry<KIND, 128, 64, A_PLANES, OutT>();
 }
 
-template <int KIND> KernelEntry pick_float_out(int type_out, int bn, int sw) {
+template <int KIND> KernelEntry pick_float_out(int type_out, int bn, int sw, bool pair) {
   switch (type_out) {
   case CCGLIB_B200_FLOAT32:
-    return pick_tile<KIND, 2, float>(bn, sw);
+    return pick_tile<KIND, 2, float>(bn, sw, pair);
   case CCGLIB_B200_FLOAT16:
-    return pick_tile<KIND, 2, __half>(bn, sw);
+    return pick_tile<KIND, 2, __half>(bn, sw, pair);
   case CCGLIB_B200_BFLOAT16:
-    return pick_tile<KIND, 2, __nv_bfloat16>(bn, sw);
+    return pick_tile<KIND, 2, __nv_bfloat16>(bn, sw, pair);
   default:
-    return {nullptr, 0};
+    return {nullptr, 0, false, false};
   }
 }
 
@@ -709,6 +980,7 @@ struct ccglib_b200_gemm_plan {
   ccglib_b200_gemm_desc desc;
   KernelEntry kernel;
   int bn, sw, a_planes;
+  int max_clusters;       // CTA-pair kernels: co-resident clusters of two
   int stage_mode;
   size_t k_bytes;         // bytes per operand row as the kernel reads it (before any padding)
   size_t pitch;           // row pitch in bytes of what the kernel reads (basic layout)
@@ -876,32 +1148,60 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
     set_last_error("CCGLIB_B200_BN must be 128 or 256 and CCGLIB_B200_SW 64 or 128");
     return CCGLIB_B200_INVALID_ARGUMENT;
   }
+  // CTA pairs (cta_group::2, 256-row tiles) are opt-in: they reach a higher tensor-pipe duty cycle
+  // per clock (95.8 % against 86 % on 8192^3 f16) but draw more power per flop (half of B comes
+  // over the SM-to-SM network), so under the 1 kW cap the clock falls further than the duty
+  // cycle rises (990 against 1312 MHz; 1150 against 1369 TFLOP/s), and in short, clock-unlimited
+  // runs they were 1-9 % slower as well.
+  const bool pair = env_int("CCGLIB_B200_PAIR", 0) != 0 && sw == 128 && d.m > kBlockM;
   plan.bn = bn;
   plan.sw = sw;
   switch (kind) {
   case kKindF16:
-    plan.kernel = pick_float_out<kKindF16>(d.type_out, bn, sw);
+    plan.kernel = pick_float_out<kKindF16>(d.type_out, bn, sw, pair);
     break;
   case kKindTF32:
-    plan.kernel = pick_float_out<kKindTF32>(d.type_out, bn, sw);
+    plan.kernel = pick_float_out<kKindTF32>(d.type_out, bn, sw, pair);
     break;
   case kKindF8F6F4:
-    plan.kernel = pick_tile<kKindF8F6F4, 2, float>(bn, sw);
+    plan.kernel = pick_tile<kKindF8F6F4, 2, float>(bn, sw, pair);
     break;
   default:
-    plan.kernel = pick_tile<kKindI8, 3, int>(bn, sw);
+    plan.kernel = pick_tile<kKindI8, 3, int>(bn, sw, pair);
     break;
   }
   if (plan.kernel.fn == nullptr) {
     set_last_error("no kernel instance for this type combination");
     return CCGLIB_B200_UNSUPPORTED;
   }
+  const uint32_t mma_m = plan.kernel.pair ? 2 * kBlockM : kBlockM;
   plan.idesc = (d_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) |
-               (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+               (static_cast<uint32_t>(bn >> 3) << 17) | ((mma_m >> 4) << 24);
   plan.idesc_neg_a = plan.idesc | (1u << 13);
   CCGLIB_CUDA_TRY(cudaFuncSetAttribute(reinterpret_cast<const void *>(plan.kernel.fn),
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        plan.kernel.smem));
+  if (plan.kernel.pair) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(plan.sms & ~1));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = plan.kernel.smem;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    CCGLIB_CUDA_TRY(cudaOccupancyMaxActiveClusters(
+        &clusters, reinterpret_cast<const void *>(plan.kernel.fn), &cfg));
+    if (clusters < 1) {
+      set_last_error("gemm_plan_create: the device cannot co-schedule a CTA pair");
+      return CCGLIB_B200_UNSUPPORTED;
+    }
+    plan.max_clusters = clusters;
+  }
 
   // ---- scratch for the staged modes, processed in batch chunks of bounded size
   plan.batch_chunk = d.batch;
@@ -951,9 +1251,11 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
   GemmParams p{};
   p.M = static_cast<uint32_t>(d.m);
   p.N = static_cast<uint32_t>(d.n);
-  p.tiles_m = static_cast<uint32_t>(ceil_div<size_t>(d.m, kBlockM));
+  const bool pair = plan.kernel.pair;
+  p.tiles_m = static_cast<uint32_t>(ceil_div<size_t>(d.m, pair ? 2 * kBlockM : kBlockM));
   p.tiles_n = static_cast<uint32_t>(ceil_div<size_t>(d.n, plan.bn));
-  p.group_n = plan.bn == 256 ? 8 : 16;
+  p.group_n = static_cast<uint32_t>(env_int("CCGLIB_B200_GROUP", plan.bn == 256 ? 8 : 16));
+  if (p.group_n == 0) p.group_n = 1;
   const size_t tiles = nb * p.tiles_m * p.tiles_n;
   if (tiles > 0x7FFFFFFFull) {
     set_last_error("gemm_run: too many tiles");
@@ -977,7 +1279,7 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
                   kSlabRowBytes * kSlabRowsA, plan.sw, kBlockM, 2);
     if (rc != CCGLIB_B200_OK) return rc;
     rc = make_map(&tm_b, b, kSlabRowBytes, kSlabRowsB, 2 * nb * slabs_n * slabs_k, kSlabRowBytes,
-                  kSlabRowBytes * kSlabRowsB, plan.sw, plan.bn, 2);
+                  kSlabRowBytes * kSlabRowsB, plan.sw, pair ? plan.bn / 2 : plan.bn, 2);
     if (rc != CCGLIB_B200_OK) return rc;
   } else {
     p.k_blocks = static_cast<uint32_t>(ceil_div<size_t>(plan.k_bytes, plan.sw));
@@ -985,7 +1287,7 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
                   plan.sw, kBlockM, plan.a_planes);
     if (rc != CCGLIB_B200_OK) return rc;
     rc = make_map(&tm_b, b, plan.k_bytes, d.n, 2 * nb, plan.pitch, plan.pitch * d.n, plan.sw,
-                  plan.bn, 2);
+                  pair ? plan.bn / 2 : plan.bn, 2);
     if (rc != CCGLIB_B200_OK) return rc;
   }
   p.idesc = plan.idesc;
@@ -1015,6 +1317,25 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
   }
   if (cudaGetSymbolAddress(reinterpret_cast<void **>(&p.status), g_device_status) != cudaSuccess) {
     return cuda_fail(cudaGetLastError(), "cudaGetSymbolAddress(g_device_status)");
+  }
+  if (pair) {
+    const size_t clusters = tiles < static_cast<size_t>(plan.max_clusters)
+                                ? tiles
+                                : static_cast<size_t>(plan.max_clusters);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = plan.kernel.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    CCGLIB_CUDA_TRY(cudaLaunchKernelEx(&cfg, plan.kernel.fn, tm_a, tm_b, tm_c, p));
+    return CCGLIB_B200_OK;
   }
   const unsigned grid = static_cast<unsigned>(tiles < static_cast<size_t>(plan.sms) ? tiles
                                                                                    : plan.sms);

@@ -174,16 +174,21 @@ def test_all_ones_known_answer(type_in):
 
 
 @pytest.mark.parametrize("bn", [128, 256])
-@pytest.mark.parametrize("sw", [64, 128])
-@pytest.mark.parametrize("types", [(ou.F16, ou.F32), (ou.INT1, ou.INT32), (ou.E4M3, ou.F32)],
-                         ids=["f16", "int1", "e4m3"])
-def test_every_tile_configuration(types, sw, bn, monkeypatch):
-    """The tile width (128/256 columns) and stage row width (64/128 bytes) are chosen by a
-    heuristic; force each combination on a multi-tile, multi-k-block, ragged problem."""
+@pytest.mark.parametrize("sw_pair", [(64, 0), (128, 0), (128, 1)],
+                         ids=["sw64", "sw128", "sw128-pair"])
+@pytest.mark.parametrize("types", [(ou.F16, ou.F32), (ou.INT1, ou.INT32), (ou.E4M3, ou.F32),
+                                   (ou.F32, ou.F16)],
+                         ids=["f16", "int1", "e4m3", "tf32-f16"])
+def test_every_tile_configuration(types, sw_pair, bn, monkeypatch):
+    """The tile width (128/256 columns), the stage row width (64/128 bytes) and whether two CTAs
+    work as a pair on a 256-row tile are chosen by heuristics; force each combination on a
+    multi-tile, multi-k-block, ragged problem (odd number of 128-row blocks included)."""
+    sw, pair = sw_pair
     monkeypatch.setenv("CCGLIB_B200_BN", str(bn))
     monkeypatch.setenv("CCGLIB_B200_SW", str(sw))
+    monkeypatch.setenv("CCGLIB_B200_PAIR", str(pair))
     type_in, type_out = types
-    B, M, N = 2, 300, 520
+    B, M, N = 2, 300, 520  # 3 blocks of 128 rows: the second CTA pair is half empty
     K = 1056 if type_in == ou.INT1 else 712
     a, b = make_inputs(22, type_in, B, M, N, K, dist="uniform")
     for variant in (capi.BASIC, capi.OPT):
