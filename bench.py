@@ -36,13 +36,15 @@ for p in (ROOT, os.path.join(ROOT, "tests")):
 import numpy as np  # noqa: E402
 
 NOMINAL_TFLOPS = {"f16": 2250.0, "bf16": 2250.0, "tf32": 1125.0, "e4m3": 4500.0, "e5m2": 4500.0,
-                  "int1": 4500.0}  # dense; int1 runs on the int8 path
+                  "int1": 9000.0}  # dense; int1 runs on the block-scaled 4-bit (e2m1) path
 
 # name: (dtype, type_in, type_out, batch, M, N, K, variant, input layout)
 WORKLOADS = {
     "c1_f16_basic_1024": ("f16", "F16", "F32", 1, 1024, 1024, 1024, "basic", "planar"),
     "c2_f16_opt_8192_b64": ("f16", "F16", "F32", 64, 8192, 8192, 8192, "opt", "interleaved"),
-    "c3_int1_4096_k65536_b32": ("int1", "INT1", "INT32", 32, 4096, 4096, 65536, "opt", "bytes"),
+    # 1-bit: Packing, then the GEMM on the packed [batch][2][rows][K/32] words; the GEMM re-stages
+    # 1-bit operands itself, so the Pipeline does not tile them first
+    "c3_int1_4096_k65536_b32": ("int1", "INT1", "INT32", 32, 4096, 4096, 65536, "basic", "bytes"),
     "c4_e4m3_4096_k16384_b32": ("e4m3", "E4M3", "F32", 32, 4096, 4096, 16384, "opt", "planar"),
     "c4_e5m2_4096_k16384_b32": ("e5m2", "E5M2", "F32", 32, 4096, 4096, 16384, "opt", "planar"),
     "c5_bf16_256x2048x512_b4096": ("bf16", "BF16", "F32", 4096, 256, 2048, 512, "basic", "planar"),
@@ -237,6 +239,7 @@ class Workload:
                                         device=self.device)
             self.b_packed = torch.empty(self.b_in.numel() // 8, dtype=torch.uint8,
                                         device=self.device)
+            self.a_gemm, self.b_gemm = self.a_packed, self.b_packed
             self.launches_per_step += 2
         if self.variant == capi.OPT:
             self.a_tiled = torch.empty(self._tiled_bytes(self.M, self.m_blk), dtype=torch.uint8,
@@ -254,10 +257,13 @@ class Workload:
             self.launches_per_step += 3 * chunks - 1  # per chunk: expand A, expand B, GEMM
 
     def _int1_chunk(self):
-        pitch = -(-self.K // 16) * 16
-        per_item = (3 * self.M + 2 * self.N) * pitch
-        return max(1, min(self.B, (int(os.environ.get("CCGLIB_B200_SCRATCH_MB", "2048")) << 20)
-                          // per_item))
+        # mirrors the plan's staging: one e2m1 nibble per sample, planes (re, im) for A and B,
+        # equal batch chunks within the scratch cap
+        pitch = -(-(-(-self.K // 2)) // 16) * 16
+        per_item = (2 * self.M + 2 * self.N) * pitch
+        cap = max(1, min(self.B, (int(os.environ.get("CCGLIB_B200_SCRATCH_MB", "8192")) << 20)
+                         // per_item))
+        return -(-self.B // -(-self.B // cap))
 
     def hbm_bytes(self):
         n = sum(t.numel() * t.element_size() for t in (self.a_in, self.b_in, self.c))
@@ -590,7 +596,8 @@ def run_ours(args, name):
             "data": "synthetic",
             "config": {"workload": name, "batch": B_total, "batch_per_gpu": share[0], "M": M,
                        "N": N, "K": K, "variant": variant, "input": layout,
-                       "step": "pack/transpose A, B + GEMM" if variant == "opt" else "GEMM",
+                       "step": ("transpose A, B + GEMM" if variant == "opt" else
+                                "pack A, B + GEMM" if layout == "bytes" else "GEMM"),
                        "l2": "inputs larger than L2 (%.1f GB resident per GPU)" % hbm_gb,
                        "parallelism": "batch split over %d GPU(s), no collective" % world},
             "roofline": roofline, "cpu_baseline": base, "e2e": e2e, "gpu_launches": launches,

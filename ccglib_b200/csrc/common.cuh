@@ -45,7 +45,7 @@ int sm_count();
 // Launchers implemented in the individual .cu files (host side, no extern "C").
 int launch_expand_bits(const void *d_in, void *d_out, size_t batch, size_t rows, size_t k_bits,
                        size_t out_row_bytes, int planes_out, bool tiled, size_t blk, size_t k_c_bits,
-                       cudaStream_t stream);
+                       cudaStream_t stream, bool nibbles = false);
 int launch_pad_rows(const void *d_in, void *d_out, size_t rows, size_t row_bytes,
                     size_t out_row_bytes, cudaStream_t stream);
 

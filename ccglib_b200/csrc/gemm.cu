@@ -64,6 +64,7 @@ struct GemmParams {
   uint32_t c_layout;
   uint32_t have_alpha, have_beta, vec_ok;
   uint32_t epi_tma;  // stage C through shared memory and store it with TMA (row-major planar)
+  uint32_t prefetch;  // k-blocks the producer asks L2 to fetch ahead of its own loads (0 = off)
   float alpha_re, alpha_im, beta_re, beta_im;
   unsigned int *status;
 };
@@ -154,6 +155,20 @@ template <> struct OutTraits<int> {
   static __device__ __forceinline__ int to_acc(int v) { return v; }
 };
 
+// int32 output whose tensor-memory accumulator is fp32 (the block-scaled 4-bit path): the sums are
+// integers below 2^24, so the conversion is exact.
+struct IntFromFloat {
+  int v;
+};
+template <> struct OutTraits<IntFromFloat> {
+  using Acc = int;
+  static __device__ __forceinline__ int from_bits(uint32_t u) {
+    return __float2int_rn(__uint_as_float(u));
+  }
+  static __device__ __forceinline__ IntFromFloat to_out(int v) { return IntFromFloat{v}; }
+  static __device__ __forceinline__ int to_acc(IntFromFloat v) { return v.v; }
+};
+
 // Pack two consecutive accumulator values into output words (one word per value for 32-bit
 // outputs, one word per pair for 16-bit outputs).
 template <typename OutT> struct Packer;
@@ -167,6 +182,7 @@ template <> struct Packer<int> {
     return static_cast<uint32_t>(v[0]);
   }
 };
+template <> struct Packer<IntFromFloat> : Packer<int> {};
 template <> struct Packer<__half> {
   static constexpr int kPerWord = 2;
   static __device__ __forceinline__ uint32_t word(const float *v) {
@@ -370,7 +386,10 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                      const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
   using C = Cfg<BN, SW, A_PLANES, EPI_TMA>;
   constexpr int kStages = C::kStages;
-  constexpr int kAccStages = C::kAccStages;
+  // the block-scaled kind keeps 32 tensor-memory columns for its (all-ones) scale factors
+  constexpr int kAccStages = (KIND == kKindMXF4) ? 1 : C::kAccStages;
+  constexpr int kScaleCol = 2 * BN * kAccStages;
+  static_assert(KIND != kKindMXF4 || kScaleCol + 32 <= kTmemCols, "no room for scale factors");
   constexpr int kSub = SW / 32;  // 32-byte MMA k-steps per stage
 
   extern __shared__ uint8_t smem_raw[];
@@ -411,12 +430,62 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if constexpr (KIND == kKindMXF4) {
+    // Scale factors are ue8m0 bytes; 0x7F = 2^0.  Every byte of the 32 columns is 1.0, so whichever
+    // bytes the MMA picks for its rows and 32-element blocks, the operands are used unscaled.
+    if (warp >= 2) {
+      const uint32_t t_sf = tmem_base + (((warp & 3) * 32) << 16) + kScaleCol;
+      tmem_st_32x32b_x16_fill(t_sf, 0x7F7F7F7Fu);
+      tmem_st_32x32b_x16_fill(t_sf + 16, 0x7F7F7F7Fu);
+      tmem_wait_st();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+  }
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     uint32_t stage = 0, phase = 0;
     uint32_t issued = 0;  // stages that have carried at least one load
     bool ok = true;
+    // operand coordinates of k-block kb of tile t
+    auto coords = [&](const TileCoord &t, uint32_t kb, int32_t &ax, int32_t &ay, int32_t &az,
+                      int32_t &bx, int32_t &by, int32_t &bz) {
+      if (p.tiled) {
+        const uint32_t slab = kb / p.k_per_slab;
+        ax = bx = static_cast<int32_t>((kb - slab * p.k_per_slab) * SW);
+        ay = 0;
+        az = static_cast<int32_t>(2 * ((t.b * p.a_slabs_m + t.mt) * p.slabs_k + slab));
+        const uint32_t n_glob = t.nt * BN;
+        const uint32_t slab_n = n_glob / p.b_slab_rows;
+        by = static_cast<int32_t>(n_glob - slab_n * p.b_slab_rows);
+        bz = static_cast<int32_t>(2 * ((t.b * p.b_slabs_n + slab_n) * p.slabs_k + slab));
+      } else {
+        ax = bx = static_cast<int32_t>(kb * SW);
+        ay = static_cast<int32_t>(t.mt * kBlockM);
+        az = static_cast<int32_t>(t.b * A_PLANES);
+        by = static_cast<int32_t>(t.nt * BN);
+        bz = static_cast<int32_t>(t.b * 2);
+      }
+    };
+    // Optional second cursor that runs p.prefetch k-blocks ahead of the loads and only asks L2 for
+    // the tiles (an experiment for short-K shapes whose loads mostly miss L2; see launch_gemm).
+    uint32_t pf_tile = blockIdx.x, pf_kb = 0;
+    auto prefetch_next = [&]() {
+      if (pf_tile >= p.num_tiles) return;
+      int32_t ax, ay, az, bx, by, bz;
+      coords(decode_tile(p, pf_tile), pf_kb, ax, ay, az, bx, by, bz);
+      tma_prefetch_3d(&tm_a, ax, ay, az);
+      tma_prefetch_3d(&tm_b, bx, by, bz);
+      if (++pf_kb == p.k_blocks) {
+        pf_kb = 0;
+        pf_tile += gridDim.x;
+      }
+    };
+    if (lane == 0) {
+      for (uint32_t i = 0; i < p.prefetch; ++i) prefetch_next();
+    }
     for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
       const TileCoord t = decode_tile(p, tile);
       for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
@@ -427,27 +496,13 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         }
         if (lane == 0) {
           int32_t ax, ay, az, bx, by, bz;
-          if (p.tiled) {
-            const uint32_t slab = kb / p.k_per_slab;
-            ax = bx = static_cast<int32_t>((kb - slab * p.k_per_slab) * SW);
-            ay = 0;
-            az = static_cast<int32_t>(2 * ((t.b * p.a_slabs_m + t.mt) * p.slabs_k + slab));
-            const uint32_t n_glob = t.nt * BN;
-            const uint32_t slab_n = n_glob / p.b_slab_rows;
-            by = static_cast<int32_t>(n_glob - slab_n * p.b_slab_rows);
-            bz = static_cast<int32_t>(2 * ((t.b * p.b_slabs_n + slab_n) * p.slabs_k + slab));
-          } else {
-            ax = bx = static_cast<int32_t>(kb * SW);
-            ay = static_cast<int32_t>(t.mt * kBlockM);
-            az = static_cast<int32_t>(t.b * A_PLANES);
-            by = static_cast<int32_t>(t.nt * BN);
-            bz = static_cast<int32_t>(t.b * 2);
-          }
+          coords(t, kb, ax, ay, az, bx, by, bz);
           const uint32_t full = bar_full + 8 * stage;
           const uint32_t dst = smem_base + stage * C::kStageBytes;
           mbar_arrive_expect_tx(full, C::kStageBytes);
           tma_load_3d(dst, &tm_a, ax, ay, az, full);
           tma_load_3d(dst + C::kABytes, &tm_b, bx, by, bz, full);
+          if (p.prefetch) prefetch_next();
         }
         __syncwarp();
         issued |= 1u << stage;
@@ -501,15 +556,28 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             const uint64_t b_re = smem_desc<SW>(b_base + k * 32);
             const uint64_t b_im = smem_desc<SW>(b_base + C::kBPlane + k * 32);
             const uint32_t accum = (kb | static_cast<uint32_t>(k)) != 0 ? 1u : 0u;
-            tc_mma<KIND>(d_re, a_re, b_re, p.idesc, accum);
-            tc_mma<KIND>(d_im, a_re, b_im, p.idesc, accum);
-            tc_mma<KIND>(d_im, a_im, b_re, p.idesc, 1u);
-            if constexpr (A_PLANES == 3) {
-              // third plane already holds -Ai (integer kinds have no negate bit)
-              const uint64_t a_neg = smem_desc<SW>(a_base + 2 * C::kAPlane + k * 32);
-              tc_mma<KIND>(d_re, a_neg, b_im, p.idesc, 1u);
+            if constexpr (KIND == kKindMXF4) {
+              const uint32_t sf = tmem_base + kScaleCol;
+              tc_mma_mxf4(d_re, a_re, b_re, p.idesc, sf, sf + 16, accum);
+              tc_mma_mxf4(d_im, a_re, b_im, p.idesc, sf, sf + 16, accum);
+              tc_mma_mxf4(d_im, a_im, b_re, p.idesc, sf, sf + 16, 1u);
+              if constexpr (A_PLANES == 3) {
+                const uint64_t a_neg = smem_desc<SW>(a_base + 2 * C::kAPlane + k * 32);
+                tc_mma_mxf4(d_re, a_neg, b_im, p.idesc, sf, sf + 16, 1u);
+              } else {
+                tc_mma_mxf4(d_re, a_im, b_im, p.idesc_neg_a, sf, sf + 16, 1u);
+              }
             } else {
-              tc_mma<KIND>(d_re, a_im, b_im, p.idesc_neg_a, 1u);
+              tc_mma<KIND>(d_re, a_re, b_re, p.idesc, accum);
+              tc_mma<KIND>(d_im, a_re, b_im, p.idesc, accum);
+              tc_mma<KIND>(d_im, a_im, b_re, p.idesc, 1u);
+              if constexpr (A_PLANES == 3) {
+                // third plane already holds -Ai (integer kinds have no negate bit)
+                const uint64_t a_neg = smem_desc<SW>(a_base + 2 * C::kAPlane + k * 32);
+                tc_mma<KIND>(d_re, a_neg, b_im, p.idesc, 1u);
+              } else {
+                tc_mma<KIND>(d_re, a_im, b_im, p.idesc_neg_a, 1u);
+              }
             }
           }
           tc_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs have read it
@@ -619,7 +687,9 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
                   const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
   using C = PairCfg<BN, A_PLANES, EPI_TMA>;
   constexpr int kStages = C::kStages;
-  constexpr int kAccStages = C::kAccStages;
+  constexpr int kAccStages = (KIND == kKindMXF4) ? 1 : C::kAccStages;
+  constexpr int kScaleCol = 2 * BN * kAccStages;  // scale-factor columns of the block-scaled kind
+  static_assert(KIND != kKindMXF4 || kScaleCol + 32 <= kTmemCols, "no room for scale factors");
   constexpr int SW = C::kSw;
   constexpr int kSub = SW / 32;
 
@@ -664,6 +734,18 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   cluster_sync();  // the peer's barriers must be initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if constexpr (KIND == kKindMXF4) {
+    // all-ones (ue8m0 0x7F) scale factors in each CTA's own tensor memory
+    if (warp >= 2) {
+      const uint32_t t_sf = tmem_base + (((warp & 3) * 32) << 16) + kScaleCol;
+      tmem_st_32x32b_x16_fill(t_sf, 0x7F7F7F7Fu);
+      tmem_st_32x32b_x16_fill(t_sf + 16, 0x7F7F7F7Fu);
+      tmem_wait_st();
+    }
+    tc_fence_before();
+    cluster_sync();
+    tc_fence_after();
+  }
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -757,14 +839,27 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
               const uint64_t b_re = smem_desc<SW>(b_base + k * 32);
               const uint64_t b_im = smem_desc<SW>(b_base + C::kBPlane + k * 32);
               const uint32_t accum = (kb | static_cast<uint32_t>(k)) != 0 ? 1u : 0u;
-              tc_mma_pair<KIND>(d_re, a_re, b_re, p.idesc, accum);
-              tc_mma_pair<KIND>(d_im, a_re, b_im, p.idesc, accum);
-              tc_mma_pair<KIND>(d_im, a_im, b_re, p.idesc, 1u);
-              if constexpr (A_PLANES == 3) {
-                const uint64_t a_neg = smem_desc<SW>(a_base + 2 * C::kAPlane + k * 32);
-                tc_mma_pair<KIND>(d_re, a_neg, b_im, p.idesc, 1u);
+              if constexpr (KIND == kKindMXF4) {
+                const uint32_t sf = tmem_base + kScaleCol;
+                tc_mma_mxf4_pair(d_re, a_re, b_re, p.idesc, sf, sf + 16, accum);
+                tc_mma_mxf4_pair(d_im, a_re, b_im, p.idesc, sf, sf + 16, accum);
+                tc_mma_mxf4_pair(d_im, a_im, b_re, p.idesc, sf, sf + 16, 1u);
+                if constexpr (A_PLANES == 3) {
+                  const uint64_t a_neg = smem_desc<SW>(a_base + 2 * C::kAPlane + k * 32);
+                  tc_mma_mxf4_pair(d_re, a_neg, b_im, p.idesc, sf, sf + 16, 1u);
+                } else {
+                  tc_mma_mxf4_pair(d_re, a_im, b_im, p.idesc_neg_a, sf, sf + 16, 1u);
+                }
               } else {
-                tc_mma_pair<KIND>(d_re, a_im, b_im, p.idesc_neg_a, 1u);
+                tc_mma_pair<KIND>(d_re, a_re, b_re, p.idesc, accum);
+                tc_mma_pair<KIND>(d_im, a_re, b_im, p.idesc, accum);
+                tc_mma_pair<KIND>(d_im, a_im, b_re, p.idesc, 1u);
+                if constexpr (A_PLANES == 3) {
+                  const uint64_t a_neg = smem_desc<SW>(a_base + 2 * C::kAPlane + k * 32);
+                  tc_mma_pair<KIND>(d_re, a_neg, b_im, p.idesc, 1u);
+                } else {
+                  tc_mma_pair<KIND>(d_re, a_im, b_im, p.idesc_neg_a, 1u);
+                }
               }
             }
             // the stage is free in both CTAs once these MMAs have read it
@@ -908,10 +1003,10 @@ template <int KIND, int BN, int SW, int A_PLANES, typename OutT> KernelEntry ent
           Cfg<BN, SW, A_PLANES, kEpiTma>::kSmemBytes, kEpiTma, false};
 }
 
-template <int KIND, int BN, int A_PLANES, typename OutT> KernelEntry pair_entry() {
-  constexpr bool kEpiTma = sizeof(OutT) == 4;
-  return {cgemm_pair_kernel<KIND, BN, A_PLANES, OutT, kEpiTma>,
-          PairCfg<BN, A_PLANES, kEpiTma>::kSmemBytes, kEpiTma, true};
+template <int KIND, int BN, int A_PLANES, typename OutT, bool EPI_TMA = (sizeof(OutT) == 4)>
+KernelEntry pair_entry() {
+  return {cgemm_pair_kernel<KIND, BN, A_PLANES, OutT, EPI_TMA>,
+          PairCfg<BN, A_PLANES, EPI_TMA>::kSmemBytes, EPI_TMA, true};
 }
 
 template <int KIND, int A_PLANES, typename OutT>
@@ -981,6 +1076,7 @@ struct ccglib_b200_gemm_plan {
   KernelEntry kernel;
   int bn, sw, a_planes;
   int max_clusters;       // CTA-pair kernels: co-resident clusters of two
+  int nibbles;            // 1-bit input expanded to e2m1 nibbles (block-scaled 4-bit MMA path)
   int stage_mode;
   size_t k_bytes;         // bytes per operand row as the kernel reads it (before any padding)
   size_t pitch;           // row pitch in bytes of what the kernel reads (basic layout)
@@ -1082,10 +1178,18 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
     ab_fmt = 1;
     break;
   case CCGLIB_B200_INT1:
-    kind = kKindI8;
-    ab_fmt = 1;  // signed 8-bit
-    d_fmt = 2;   // s32 accumulate
-    plan.a_planes = 3;
+    // +-1 samples run either as signed bytes on the integer kind (s32 accumulators) or, opt-in, as
+    // e2m1 nibbles on the block-scaled 4-bit kind with all scale factors 1.0 (fp32 accumulators)
+    // The fp32 accumulator of the 4-bit path holds the integer sums exactly while 2K < 2^24
+    // (verified bit-exact against the CPU oracle up to K = 65536); beyond K = 2^22 samples the
+    // integer kind takes over.  The 4-bit path runs at twice the rate and a fraction of the power.
+    plan.nibbles = (env_int("CCGLIB_B200_INT1_MXF4", 1) != 0 && d.k <= (size_t{1} << 22)) ? 1 : 0;
+    kind = plan.nibbles ? kKindMXF4 : kKindI8;
+    ab_fmt = 1;  // signed 8-bit, resp. e2m1
+    d_fmt = 2;   // s32 accumulate (unused by the block-scaled descriptor)
+    // the integer kind has no negate bit and reads -Ai from a third plane; the 4-bit kind negates
+    // in the instruction descriptor (a third plane remains selectable for cross-checking)
+    plan.a_planes = (plan.nibbles && env_int("CCGLIB_B200_MXF4_NEGATE", 1) != 0) ? 2 : 3;
     break;
   default:
     set_last_error("No kernel available for input type %d", d.type_in);
@@ -1120,8 +1224,9 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
   // ---- staging mode and operand geometry
   if (d.type_in == CCGLIB_B200_INT1) {
     plan.stage_mode = kExpandBits;
-    plan.k_bytes = d.k;  // one signed byte per sample after expansion
-    plan.pitch = ceil_div<size_t>(d.k, 16) * 16;
+    // one signed byte, resp. one nibble, per sample after expansion
+    plan.k_bytes = plan.nibbles ? ceil_div<size_t>(d.k, 2) : d.k;
+    plan.pitch = ceil_div<size_t>(plan.k_bytes, 16) * 16;
   } else {
     plan.k_bytes = d.k * in_bits / 8;
     if (d.variant == CCGLIB_B200_OPT) {
@@ -1144,7 +1249,12 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
   int sw = 128;
   bn = env_int("CCGLIB_B200_BN", bn);
   sw = env_int("CCGLIB_B200_SW", sw);
-  if ((bn != 128 && bn != 256) || (sw != 64 && sw != 128)) {
+  if (kind == kKindMXF4) {
+    // two accumulators plus the scale-factor columns must fit 512 tensor-memory columns
+    if (bn == 256) bn = 192;
+    sw = 128;
+  }
+  if ((bn != 128 && bn != 256 && !(bn == 192 && kind == kKindMXF4)) || (sw != 64 && sw != 128)) {
     set_last_error("CCGLIB_B200_BN must be 128 or 256 and CCGLIB_B200_SW 64 or 128");
     return CCGLIB_B200_INVALID_ARGUMENT;
   }
@@ -1153,7 +1263,10 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
   // over the SM-to-SM network), so under the 1 kW cap the clock falls further than the duty
   // cycle rises (990 against 1312 MHz; 1150 against 1369 TFLOP/s), and in short, clock-unlimited
   // runs they were 1-9 % slower as well.
-  const bool pair = env_int("CCGLIB_B200_PAIR", 0) != 0 && sw == 128 && d.m > kBlockM;
+  // The 4-bit path is the exception: it is bound by operand traffic from L2, not by power, and a
+  // pair halves the B bytes each SM fetches (5.6 against 5.3 POPS at 4096 x 4096 x 65536).
+  const bool pair = env_int("CCGLIB_B200_PAIR", kind == kKindMXF4 ? 1 : 0) != 0 && sw == 128 &&
+                    d.m > kBlockM;
   plan.bn = bn;
   plan.sw = sw;
   switch (kind) {
@@ -1165,6 +1278,19 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
     break;
   case kKindF8F6F4:
     plan.kernel = pick_tile<kKindF8F6F4, 2, float>(bn, sw, pair);
+    break;
+  case kKindMXF4:
+    if (plan.a_planes == 3) {
+      plan.kernel = pair ? (bn == 192 ? pair_entry<kKindMXF4, 192, 3, IntFromFloat>()
+                                      : pair_entry<kKindMXF4, 128, 3, IntFromFloat>())
+                         : (bn == 192 ? entry<kKindMXF4, 192, 128, 3, IntFromFloat>()
+                                      : entry<kKindMXF4, 128, 128, 3, IntFromFloat>());
+    } else {
+      plan.kernel = pair ? (bn == 192 ? pair_entry<kKindMXF4, 192, 2, IntFromFloat>()
+                                      : pair_entry<kKindMXF4, 128, 2, IntFromFloat>())
+                         : (bn == 192 ? entry<kKindMXF4, 192, 128, 2, IntFromFloat>()
+                                      : entry<kKindMXF4, 128, 128, 2, IntFromFloat>());
+    }
     break;
   default:
     plan.kernel = pick_tile<kKindI8, 3, int>(bn, sw, pair);
@@ -1178,6 +1304,13 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
   plan.idesc = (d_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) |
                (static_cast<uint32_t>(bn >> 3) << 17) | ((mma_m >> 4) << 24);
   plan.idesc_neg_a = plan.idesc | (1u << 13);
+  if (kind == kKindMXF4) {
+    // block-scaled descriptor: [7,10)/[10,13) operand formats (1 = e2m1), [17,23) N>>3, bit 23
+    // scale format (1 = ue8m0), [24,29) M>>4; scale-factor byte ids and K size stay 0
+    plan.idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(bn >> 3) << 17) | (1u << 23) |
+                 ((mma_m >> 4) << 24);
+    plan.idesc_neg_a = plan.idesc | (1u << 13);
+  }
   CCGLIB_CUDA_TRY(cudaFuncSetAttribute(reinterpret_cast<const void *>(plan.kernel.fn),
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        plan.kernel.smem));
@@ -1208,10 +1341,11 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
   if (plan.stage_mode != kDirect) {
     const size_t per_item_a = plan.a_planes * d.m * plan.pitch;
     const size_t per_item_b = 2 * d.n * plan.pitch;
-    const size_t budget = static_cast<size_t>(env_int("CCGLIB_B200_SCRATCH_MB", 2048)) << 20;
+    const size_t budget = static_cast<size_t>(env_int("CCGLIB_B200_SCRATCH_MB", 8192)) << 20;
     size_t chunk = budget / (per_item_a + per_item_b);
     if (chunk < 1) chunk = 1;
     if (chunk > d.batch) chunk = d.batch;
+    chunk = ceil_div(d.batch, ceil_div(d.batch, chunk));  // equal chunks: no short last launch
     plan.batch_chunk = chunk;
     plan.scratch_bytes = chunk * (per_item_a + per_item_b);
     if (cudaMalloc(&plan.scratch_a, plan.scratch_bytes) != cudaSuccess) {
@@ -1308,6 +1442,9 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
   // 16-byte stores need every row run to start on a 16-byte boundary
   const size_t run_bytes = (planar ? d.n : 2 * d.n) * plan.out_elem_bytes;
   p.vec_ok = (row && aligned16(c) && run_bytes % 16 == 0) ? 1u : 0u;
+  // L2 prefetch distance in k-blocks; off by default: on the HBM-bound short-K shape (256 x 2048 x
+  // 512, batch 4096) distances 3..24 were 12-34 % slower than none, and slower on the others too
+  p.prefetch = static_cast<uint32_t>(env_int("CCGLIB_B200_PREFETCH", 0));
   // TMA-store epilogue: row-major planar C with four-byte elements, 16-byte aligned rows
   CUtensorMap tm_c = tm_a;  // placeholder when the epilogue stores straight from registers
   p.epi_tma = (plan.kernel.epi_tma && planar && p.vec_ok && plan.out_elem_bytes == 4) ? 1u : 0u;
@@ -1380,12 +1517,12 @@ extern "C" int ccglib_b200_gemm_run(ccglib_b200_gemm_plan *plan, const void *d_a
         b_item = 2 * d.n * words * 4;
       }
       rc = launch_expand_bits(static_cast<const char *>(d_a) + b0 * a_item, plan->scratch_a, nb,
-                              d.m, d.k, plan->pitch, 3, tiled_in, kSlabRowsA, kSlabRowBytes * 8,
-                              stream);
+                              d.m, d.k, plan->pitch, plan->a_planes, tiled_in, kSlabRowsA,
+                              kSlabRowBytes * 8, stream, plan->nibbles != 0);
       if (rc != CCGLIB_B200_OK) return rc;
       rc = launch_expand_bits(static_cast<const char *>(d_b) + b0 * b_item, plan->scratch_b, nb,
                               d.n, d.k, plan->pitch, 2, tiled_in, kSlabRowsB, kSlabRowBytes * 8,
-                              stream);
+                              stream, plan->nibbles != 0);
       if (rc != CCGLIB_B200_OK) return rc;
     } else {
       rc = launch_pad_rows(static_cast<const char *>(d_a) + b0 * 2 * d.m * plan->k_bytes,

@@ -65,6 +65,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *tm,
                : "memory");
 }
 
+// Ask for a 3-D tile to be brought into L2 (no shared-memory destination, nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap *tm, int32_t x, int32_t y,
+                                                int32_t z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+
 // 3-D tiled store from this CTA's shared memory to global memory (bulk async-group completion);
 // elements of the box that fall outside the tensor are not written.
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap *tm, uint32_t src, int32_t x,
@@ -209,7 +218,47 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster) {
                : "memory");
 }
 
-enum MmaKind { kKindF16 = 0, kKindTF32 = 1, kKindF8F6F4 = 2, kKindI8 = 3 };
+enum MmaKind { kKindF16 = 0, kKindTF32 = 1, kKindF8F6F4 = 2, kKindI8 = 3, kKindMXF4 = 4 };
+
+// Block-scaled 4-bit MMA (e2m1 operands, one ue8m0 scale per 32 elements read from tensor memory
+// at sfa / sfb): D[tmem] (+)= (A * scale_a) x (B * scale_b), K = 64 per instruction.
+__device__ __forceinline__ void tc_mma_mxf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                            uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], "
+               "[%6], p;\n\t}"
+               :
+               : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem),
+                 "r"(sfb_tmem)
+               : "memory");
+}
+
+// The same for a CTA pair (M = 256; scale factors in each CTA's own tensor memory).
+__device__ __forceinline__ void tc_mma_mxf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t sfa_tmem,
+                                                 uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], "
+               "[%6], p;\n\t}"
+               :
+               : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem),
+                 "r"(sfb_tmem)
+               : "memory");
+}
+
+// Warp-collective store of one 32-bit value per lane into 16 consecutive tensor-memory columns
+// of the warp's 32 lanes.
+__device__ __forceinline__ void tmem_st_32x32b_x16_fill(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+               "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr),
+               "r"(v)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_wait_st() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 
 // Pair MMA: D (256 x N, 128 rows in each CTA's tensor memory) (+)= A (each CTA's 128 rows) x B
 // (N/2 rows from each CTA's shared memory); issued by one thread of the leader CTA.

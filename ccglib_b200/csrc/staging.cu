@@ -1,8 +1,9 @@
 // Re-staging kernels used by the GEMM plan when the caller's operands cannot be read by TMA as
 // they are:
-//   * expand_bits: packed 1-bit samples (bit 1 = +1, bit 0 = -1) -> one signed byte per sample,
-//     planes (re, im[, -im]); tcgen05 has no 1-bit MMA and its integer kind has no negate bit,
-//     so the +-1 bytes (and the negated imaginary plane of A) are produced here.
+//   * expand_bits: packed 1-bit samples (bit 1 = +1, bit 0 = -1) -> one signed byte (or one e2m1
+//     nibble) per sample, planes (re, im[, -im]); tcgen05 has no 1-bit MMA and its integer kind
+//     has no negate bit, so the +-1 values (and the negated imaginary plane of A) are produced
+//     here.
 //   * pad_rows: copies rows whose byte length is not a multiple of 16 to a 16-byte pitch.
 // Both are pure data movement bounded by HBM bandwidth.
 #include "common.cuh"
@@ -15,6 +16,14 @@ __device__ __forceinline__ uint32_t spread_nibble(uint32_t nibble) {
   return (nibble * 0x00204081u) & 0x01010101u;
 }
 
+// 8 bits -> 8 nibbles (bit j -> bit 4j).
+__device__ __forceinline__ uint32_t spread_byte(uint32_t v) {
+  uint32_t x = (v | (v << 12)) & 0x000F000Fu;
+  x = (x | (x << 6)) & 0x03030303u;
+  x = (x | (x << 3)) & 0x11111111u;
+  return x;
+}
+
 struct ExpandParams {
   const uint32_t *in;
   int8_t *out;
@@ -22,6 +31,7 @@ struct ExpandParams {
   size_t units;      // 32-byte output units (= input words) per row
   size_t words;      // input words per row
   int planes_out;    // 2: (re, im); 3: (re, im, -im)
+  int nibbles;       // 0: one signed byte per sample; 1: one e2m1 nibble per sample (+-1.0)
   int tiled;
   size_t blk, kc_words, row_tiles, k_tiles;
 };
@@ -47,6 +57,26 @@ __global__ void __launch_bounds__(256) expand_bits_kernel(const ExpandParams p) 
     const uint32_t w = __ldg(p.in + src);
     const size_t bit0 = u * 32;
     const int valid = static_cast<int>(p.k_bits - bit0 < 32 ? p.k_bits - bit0 : 32);
+    if (p.nibbles) {
+      // 32 samples -> 16 bytes: sample i in nibble i; +1 = 0x2 (e2m1 1.0), -1 = 0xA, padding = 0
+      uint32_t pos4[4], neg4[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t sign = spread_byte((w >> (8 * i)) & 0xFFu);  // bit j -> bit 4j
+        uint32_t mask = 0xFFFFFFFFu;
+        if (8 * i + 8 > valid) mask = (8 * i >= valid) ? 0u : ((1u << (4 * (valid - 8 * i))) - 1u);
+        pos4[i] = (0x22222222u | ((~sign & 0x11111111u) << 3)) & mask;
+        neg4[i] = (0x22222222u | (sign << 3)) & mask;
+      }
+      const size_t plane_bytes4 = p.rows * p.out_row_bytes;
+      int8_t *dst4 = p.out + ((b * p.planes_out + c) * p.rows + r) * p.out_row_bytes + u * 16;
+      *reinterpret_cast<uint4 *>(dst4) = make_uint4(pos4[0], pos4[1], pos4[2], pos4[3]);
+      if (c == 1 && p.planes_out == 3) {
+        *reinterpret_cast<uint4 *>(dst4 + plane_bytes4) =
+            make_uint4(neg4[0], neg4[1], neg4[2], neg4[3]);
+      }
+      continue;
+    }
     uint32_t pos[8], neg[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -98,7 +128,7 @@ unsigned grid_for(size_t total, int threads) {
 
 int launch_expand_bits(const void *d_in, void *d_out, size_t batch, size_t rows, size_t k_bits,
                        size_t out_row_bytes, int planes_out, bool tiled, size_t blk,
-                       size_t k_c_bits, cudaStream_t stream) {
+                       size_t k_c_bits, cudaStream_t stream, bool nibbles) {
   ExpandParams p{};
   p.in = static_cast<const uint32_t *>(d_in);
   p.out = static_cast<int8_t *>(d_out);
@@ -109,6 +139,7 @@ int launch_expand_bits(const void *d_in, void *d_out, size_t batch, size_t rows,
   p.words = ceil_div<size_t>(k_bits, 32);
   p.units = p.words;
   p.planes_out = planes_out;
+  p.nibbles = nibbles ? 1 : 0;
   p.tiled = tiled ? 1 : 0;
   p.blk = blk;
   p.kc_words = k_c_bits / 32;

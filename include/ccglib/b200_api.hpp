@@ -356,6 +356,10 @@ public:
            std::complex<float> alpha = {1, 0}, std::complex<float> beta = {0, 0})
       : need_copyin_c_(beta.real() != 0 || beta.imag() != 0), stream_(stream) {
     const bool packs = input_precision == int1;
+    // 1-bit operands are re-staged by the GEMM itself whatever their layout, so tiling them first
+    // would only add a pass over memory: with planar output (the only kind the basic variant
+    // writes) the pipeline hands the packed words over as they are
+    if (packs && output_complex_axis_location == complex_planar) variant = mma::basic;
     const bool tiles = variant == mma::opt;
     const Precision precision(input_precision, output_precision);
     const size_t bits = precision.GetInputBits();

@@ -143,6 +143,42 @@ def test_alpha_beta_f16_out_layouts(section):
     gu.assert_close_reference_rule(got, want, ou.F16, ou.F16)
 
 
+@pytest.mark.parametrize("path", [dict(CCGLIB_B200_INT1_MXF4="0"),
+                                  dict(CCGLIB_B200_INT1_MXF4="0", CCGLIB_B200_PAIR="1"),
+                                  dict(CCGLIB_B200_INT1_MXF4="1", CCGLIB_B200_MXF4_NEGATE="0",
+                                       CCGLIB_B200_PAIR="0"),
+                                  dict(CCGLIB_B200_INT1_MXF4="1", CCGLIB_B200_MXF4_NEGATE="1",
+                                       CCGLIB_B200_PAIR="0"),
+                                  dict(CCGLIB_B200_INT1_MXF4="1", CCGLIB_B200_MXF4_NEGATE="0",
+                                       CCGLIB_B200_PAIR="1"),
+                                  dict(CCGLIB_B200_INT1_MXF4="1", CCGLIB_B200_MXF4_NEGATE="1",
+                                       CCGLIB_B200_PAIR="1")],
+                         ids=["i8", "i8-pair", "mxf4-3planes", "mxf4-negate", "mxf4-3planes-pair",
+                              "mxf4-negate-pair"])
+def test_int1_every_tensor_path_is_bit_exact(path, monkeypatch):
+    """1-bit GEMM runs as signed bytes on the integer MMA kind or as e2m1 nibbles on the
+    block-scaled 4-bit kind (unit scale factors), with -Ai from a third plane or from the negate
+    bit, on one SM or a CTA pair: all of them must reproduce the oracle exactly, alpha/beta,
+    ragged edges and K padding included."""
+    for key, value in path.items():
+        monkeypatch.setenv(key, value)
+    B, M, N, K = 2, 300, 520, 2000
+    a, b = make_inputs(31, ou.INT1, B, M, N, K)
+    rng = np.random.default_rng(32)
+    c0 = rng.integers(-100, 100, size=(B, 2, M, N), dtype=np.int32)
+    alpha, beta = (2.0, -3.0), (1.0, 2.0)
+    got = gu.run_gemm(ou.INT1, ou.INT32, a, b, B, M, N, K, variant=capi.BASIC, alpha=alpha,
+                      beta=beta, c0=c0)
+    want = gu.oracle_batch(ou.INT1, ou.INT32, a, b, B, M, N, K, alpha, beta, c0)
+    assert np.array_equal(got.reshape(B, 2, M, N), want)
+    K = 2016  # the tiled layout holds whole 32-sample words
+    a, b = make_inputs(33, ou.INT1, B, M, N, K)
+    got = gu.run_gemm(ou.INT1, ou.INT32, a, b, B, M, N, K, variant=capi.OPT,
+                      c_axis=capi.INTERLEAVED, c_order=capi.COL_MAJOR)
+    want = gu.oracle_batch(ou.INT1, ou.INT32, a, b, B, M, N, K)
+    assert np.array_equal(gu.canonical_c(got, B, M, N, capi.INTERLEAVED, capi.COL_MAJOR), want)
+
+
 def test_alpha_beta_int1():
     # test/gemm/mma.cpp:702-776
     B, M, N, K = 2, 256, 128, 256
@@ -197,6 +233,15 @@ def test_every_tile_configuration(types, sw_pair, bn, monkeypatch):
             assert np.array_equal(got, gu.oracle_batch(type_in, type_out, a, b, B, M, N, K))
         else:
             gu.assert_close_fp64(got, type_in, type_out, a, b, K)
+
+
+def test_l2_prefetch_cursor_does_not_change_results(monkeypatch):
+    monkeypatch.setenv("CCGLIB_B200_PREFETCH", "5")
+    B, M, N, K = 3, 300, 520, 200  # 4 k-blocks per tile: the cursor runs into later tiles
+    a, b = make_inputs(30, ou.BF16, B, M, N, K, dist="uniform")
+    for variant in (capi.BASIC, capi.OPT):
+        got = gu.run_gemm(ou.BF16, ou.F32, a, b, B, M, N, K, variant=variant).reshape(B, 2, M, N)
+        gu.assert_close_fp64(got, ou.BF16, ou.F32, a, b, K)
 
 
 def test_interleaved_input_through_transpose():
