@@ -99,6 +99,74 @@ __global__ void __launch_bounds__(256) expand_bits_kernel(const ExpandParams p) 
   }
 }
 
+// Fast path for rows of whole 128-sample groups (K % 128 == 0): one thread expands four words
+// (one 16-byte load) into 64 bytes of nibbles or 128 bytes of signed bytes, so the index
+// arithmetic is paid once per 128 samples and every store is a full 16-byte vector.
+template <bool NIBBLES>
+__global__ void __launch_bounds__(256) expand_bits_vec_kernel(const ExpandParams p) {
+  const size_t units4 = p.words / 4;
+  const size_t total = p.batch * 2 * p.rows * units4;
+  const size_t plane_bytes = p.rows * p.out_row_bytes;
+  for (size_t gid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; gid < total;
+       gid += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t u4 = gid % units4;
+    size_t t = gid / units4;
+    const size_t r = t % p.rows;
+    t /= p.rows;
+    const size_t c = t & 1;
+    const size_t b = t >> 1;
+    size_t src;
+    if (p.tiled) {
+      const size_t u = u4 * 4;
+      const size_t rt = r / p.blk, rr = r - rt * p.blk;
+      const size_t kt = u / p.kc_words, uu = u - kt * p.kc_words;
+      src = ((((b * p.row_tiles + rt) * p.k_tiles + kt) * 2 + c) * p.blk + rr) * p.kc_words + uu;
+    } else {
+      src = ((b * 2 + c) * p.rows + r) * p.words + u4 * 4;
+    }
+    const uint4 w4 = __ldg(reinterpret_cast<const uint4 *>(p.in + src));
+    const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+    const bool negated_plane = c == 1 && p.planes_out == 3;
+    if constexpr (NIBBLES) {
+      uint4 *dst = reinterpret_cast<uint4 *>(
+          p.out + ((b * p.planes_out + c) * p.rows + r) * p.out_row_bytes + u4 * 64);
+      uint4 *dneg = reinterpret_cast<uint4 *>(reinterpret_cast<int8_t *>(dst) + plane_bytes);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t pos[4], neg[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t sign = spread_byte((w[q] >> (8 * i)) & 0xFFu);
+          pos[i] = 0x22222222u | ((~sign & 0x11111111u) << 3);
+          neg[i] = 0x22222222u | (sign << 3);
+        }
+        dst[q] = make_uint4(pos[0], pos[1], pos[2], pos[3]);
+        if (negated_plane) dneg[q] = make_uint4(neg[0], neg[1], neg[2], neg[3]);
+      }
+    } else {
+      uint4 *dst = reinterpret_cast<uint4 *>(
+          p.out + ((b * p.planes_out + c) * p.rows + r) * p.out_row_bytes + u4 * 128);
+      uint4 *dneg = reinterpret_cast<uint4 *>(reinterpret_cast<int8_t *>(dst) + plane_bytes);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t pos[8], neg[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t y = spread_nibble((w[q] >> (4 * i)) & 0xFu);
+          pos[i] = 0xFFFFFFFFu - y * 0xFEu;
+          neg[i] = 0x01010101u + y * 0xFEu;
+        }
+        dst[2 * q] = make_uint4(pos[0], pos[1], pos[2], pos[3]);
+        dst[2 * q + 1] = make_uint4(pos[4], pos[5], pos[6], pos[7]);
+        if (negated_plane) {
+          dneg[2 * q] = make_uint4(neg[0], neg[1], neg[2], neg[3]);
+          dneg[2 * q + 1] = make_uint4(neg[4], neg[5], neg[6], neg[7]);
+        }
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256)
 pad_rows_kernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out, size_t rows,
                 size_t row_bytes, size_t out_row_bytes) {
@@ -120,7 +188,7 @@ pad_rows_kernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out, size_
 
 unsigned grid_for(size_t total, int threads) {
   const size_t blocks = ceil_div<size_t>(total, threads);
-  const size_t cap = static_cast<size_t>(sm_count()) * 16;
+  const size_t cap = static_cast<size_t>(sm_count()) * 32;
   return static_cast<unsigned>(blocks < cap ? (blocks ? blocks : 1) : cap);
 }
 
@@ -145,6 +213,17 @@ int launch_expand_bits(const void *d_in, void *d_out, size_t batch, size_t rows,
   p.kc_words = k_c_bits / 32;
   p.row_tiles = ceil_div<size_t>(rows, blk);
   p.k_tiles = ceil_div<size_t>(p.words, p.kc_words);
+  const bool vec = k_bits % 128 == 0 && aligned16(d_in) && (!tiled || p.kc_words % 4 == 0);
+  if (vec) {
+    const size_t total4 = batch * 2 * rows * (p.words / 4);
+    if (nibbles) {
+      expand_bits_vec_kernel<true><<<grid_for(total4, 256), 256, 0, stream>>>(p);
+    } else {
+      expand_bits_vec_kernel<false><<<grid_for(total4, 256), 256, 0, stream>>>(p);
+    }
+    CCGLIB_CUDA_TRY(cudaGetLastError());
+    return CCGLIB_B200_OK;
+  }
   const size_t total = batch * 2 * rows * p.units;
   expand_bits_kernel<<<grid_for(total, 256), 256, 0, stream>>>(p);
   CCGLIB_CUDA_TRY(cudaGetLastError());
