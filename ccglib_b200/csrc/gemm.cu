@@ -9,7 +9,7 @@
 //   warps 2..5  epilogue       -- tcgen05.ld the accumulators, apply alpha/beta, convert, and
 //                                 store planar/interleaved, row/col-major C
 // Stage hand-over uses mbarrier rings (full: TMA complete_tx, empty: tcgen05.commit); the
-// accumulator is handed to the epilogue by tcgen05.commit and back by thread arrivals.
+// accumulator is handed to the epilogue by tcgen05.commit and back by one arrival per warp.
 //
 // Every wait is bounded: a wait that runs out sets a shared abort flag and a bit in the global
 // status word, after which all roles fall through to the common tear-down (TMEM is always freed).
@@ -414,7 +414,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     }
     for (int s = 0; s < kAccStages; ++s) {
       mbar_init(bar_acc_full + 8 * s, 1);
-      mbar_init(bar_acc_empty + 8 * s, 128);
+      mbar_init(bar_acc_empty + 8 * s, 4);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -626,7 +626,8 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         epilogue_chunk<OutT>(p, t.b, m, n0, bits_re, bits_im);
       }
       tc_fence_before();
-      mbar_arrive(bar_acc_empty + 8 * acc);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
       if (++acc == kAccStages) {
         acc = 0;
         acc_phase ^= 1;
@@ -660,7 +661,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
 //
 // Hand-over: both producers arm and fill the LEADER's full barrier (2 arrivals + both CTAs' bytes;
 // loads carry .cta_group::2 so that they may signal the peer's barrier, never multicast); the
-// leader's commits arrive on each CTA's own empty / acc_full barriers; all 256 epilogue threads
+// leader's commits arrive on each CTA's own empty / acc_full barriers; the eight epilogue warps
 // of the pair arrive on the leader's acc_empty barrier.  Set-up and tear-down are cluster-wide
 // barriers, so neither CTA leaves while the other may still touch its shared memory.
 
@@ -718,7 +719,7 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
     }
     for (int s = 0; s < kAccStages; ++s) {
       mbar_init(bar_acc_full + 8 * s, 1);
-      mbar_init(bar_acc_empty + 8 * s, 256);  // epilogue threads of both CTAs (used in the leader)
+      mbar_init(bar_acc_empty + 8 * s, 8);  // epilogue warps of both CTAs (used in the leader)
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -913,7 +914,8 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         epilogue_chunk<OutT>(p, t.b, m0 + lane, n0, bits_re, bits_im);
       }
       tc_fence_before();
-      mbar_arrive_cluster(map_to_cta(bar_acc_empty + 8 * acc, 0));
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(bar_acc_empty + 8 * acc, 0));
       if (++acc == kAccStages) {
         acc = 0;
         acc_phase ^= 1;
