@@ -5,7 +5,8 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "lib", "libccglib_b200.so")
+# CCGLIB_B200_LIB selects another build of the same library (e.g. an instrumented one)
+LIB_PATH = os.environ.get("CCGLIB_B200_LIB") or os.path.join(HERE, "lib", "libccglib_b200.so")
 
 # ccglib::ValueType (reference include/ccglib/common/value_type.h:14-22)
 INT1, INT32, BFLOAT16, FLOAT8E4M3, FLOAT8E5M2, FLOAT16, FLOAT32 = range(7)

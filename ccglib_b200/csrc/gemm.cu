@@ -69,16 +69,17 @@ struct GemmParams {
   unsigned int *status;
 };
 
-constexpr int kStagingBytes = 4 * 2 * 32 * 128;  // per epilogue warp: (re, im) x 32 rows x 128 B
+constexpr int kStagingTile = 32 * 128;  // one staging tile: 32 rows x 128 B
+constexpr int kStagingBytes = 4 * 2 * kStagingTile;  // two tiles for each of the four epilogue warps
 
-template <int BN, int SW, int A_PLANES, bool EPI_TMA> struct Cfg {
+template <int BN, int SW, int A_PLANES, int EPI> struct Cfg {
   static constexpr int kAPlane = kBlockM * SW;
   static constexpr int kBPlane = BN * SW;
   static constexpr int kABytes = A_PLANES * kAPlane;
   static constexpr int kBBytes = 2 * kBPlane;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kStaging = EPI_TMA ? kStagingBytes : 0;
+  static constexpr int kStaging = 4 * EPI * kStagingTile;  // EPI tiles per epilogue warp
   static constexpr int kStagesRaw = (kMaxSmem - 1024 - kBarrierBytes - kStaging) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kAccStages = (BN == 128) ? 2 : 1;
@@ -331,16 +332,10 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, uint32_t b, 
   }
 }
 
-// One warp writes its 32 rows x 32 four-byte columns into a 4 KiB staging tile laid out the way a
-// 128-byte-swizzled TMA store reads it (16-byte chunk j of row r sits at chunk j ^ (r & 7)), then
-// lane 0 issues the store.  The tile is reused only after the previous store from it has finished
-// reading (at most one younger store, from the other plane's tile, may still be pending).
+// One lane writes its row of 32 four-byte values into a 4 KiB staging tile laid out the way a
+// 128-byte-swizzled TMA store reads it (16-byte chunk j of row r sits at chunk j ^ (r & 7)).
 template <typename Acc>
-__device__ __forceinline__ void staged_store(const CUtensorMap *tm_c, uint32_t tile, uint32_t lane,
-                                             const Acc (&v)[32], bool issue, int32_t x, int32_t y,
-                                             int32_t z) {
-  if (lane == 0) bulk_wait_group_read<1>();
-  __syncwarp();
+__device__ __forceinline__ void stage_row(uint32_t tile, uint32_t lane, const Acc (&v)[32]) {
   const uint32_t row = tile + lane * 128;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
@@ -348,43 +343,51 @@ __device__ __forceinline__ void staged_store(const CUtensorMap *tm_c, uint32_t t
                  Packer<Acc>::word(&v[4 * j + 1]), Packer<Acc>::word(&v[4 * j + 2]),
                  Packer<Acc>::word(&v[4 * j + 3]));
   }
-  fence_proxy_async_smem();
-  __syncwarp();
-  if (lane == 0 && issue) {
-    tma_store_3d(tm_c, tile, x, y, z);
-    bulk_commit_group();
-  }
 }
 
 // Epilogue for 32 rows (one per lane, first row m0) and 32 columns from n0, stored through the
-// warp's staging tiles with TMA (row-major planar C with four-byte elements).
-template <typename OutT>
+// warp's staging tiles with TMA (row-major planar C with four-byte elements).  The real and the
+// imaginary tile are written side by side, made visible to the async proxy with one fence, and
+// stored as one bulk group.  A warp rotates through DEPTH / 2 tile pairs and reuses a pair only
+// after the group issued from it has finished reading shared memory.
+template <typename OutT, int DEPTH>
 __device__ __forceinline__ void epilogue_chunk_staged(const GemmParams &p, const CUtensorMap *tm_c,
-                                                      uint32_t staging, uint32_t lane, uint32_t b,
-                                                      uint32_t m0, uint32_t n0,
-                                                      const uint32_t (&bits_re)[32],
+                                                      uint32_t staging, uint32_t &slot,
+                                                      uint32_t lane, uint32_t b, uint32_t m0,
+                                                      uint32_t n0, const uint32_t (&bits_re)[32],
                                                       const uint32_t (&bits_im)[32]) {
   using Acc = typename OutTraits<OutT>::Acc;
   static_assert(sizeof(OutT) == 4, "staged epilogue is for four-byte outputs");
+  static_assert(DEPTH >= 2 && DEPTH % 2 == 0, "staging tiles come in (re, im) pairs");
   const uint32_t m = m0 + lane;
   const int valid = static_cast<int>(min(32u, p.N - n0));
   const COffsets o = c_offsets(p, b, m, n0);
   Acc re[32], im[32];
   epilogue_values<OutT>(p, o, m < p.M, valid, bits_re, bits_im, re, im);
-  const bool issue = m0 < p.M;
-  const int32_t x = static_cast<int32_t>(n0 * 4);  // the tensor map is byte-typed
-  staged_store<Acc>(tm_c, staging, lane, re, issue, x, static_cast<int32_t>(m0),
-                    static_cast<int32_t>(2 * b));
-  staged_store<Acc>(tm_c, staging + 4096, lane, im, issue, x, static_cast<int32_t>(m0),
-                    static_cast<int32_t>(2 * b + 1));
+  const uint32_t tiles = staging + (slot % (DEPTH / 2)) * (2 * kStagingTile);
+  ++slot;
+  if (lane == 0) bulk_wait_group_read<DEPTH / 2 - 1>();
+  __syncwarp();
+  stage_row<Acc>(tiles, lane, re);
+  stage_row<Acc>(tiles + kStagingTile, lane, im);
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0 && m0 < p.M) {
+    const int32_t x = static_cast<int32_t>(n0 * 4);  // the tensor map is byte-typed
+    tma_store_3d(tm_c, tiles, x, static_cast<int32_t>(m0), static_cast<int32_t>(2 * b));
+    tma_store_3d(tm_c, tiles + kStagingTile, x, static_cast<int32_t>(m0),
+                 static_cast<int32_t>(2 * b + 1));
+    bulk_commit_group();
+  }
 }
 
-template <int KIND, int BN, int SW, int A_PLANES, typename OutT, bool EPI_TMA>
+template <int KIND, int BN, int SW, int A_PLANES, typename OutT, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                      const __grid_constant__ CUtensorMap tm_b,
                      const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
-  using C = Cfg<BN, SW, A_PLANES, EPI_TMA>;
+  using C = Cfg<BN, SW, A_PLANES, EPI>;
+  constexpr bool EPI_TMA = EPI > 0;
   constexpr int kStages = C::kStages;
   // the block-scaled kind keeps 32 tensor-memory columns for its (all-ones) scale factors
   constexpr int kAccStages = (KIND == kKindMXF4) ? 1 : C::kAccStages;
@@ -598,6 +601,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     // ------------------------------------------------------------------ epilogue warps
     const uint32_t quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
     uint32_t acc = 0, acc_phase = 0;
+    uint32_t slot = 0;  // staging tile rotation
     for (uint32_t tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
       const TileCoord t = decode_tile(p, tile);
       if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, p.status,
@@ -617,9 +621,11 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         tmem_wait_ld();
         if constexpr (EPI_TMA) {
           if (p.epi_tma) {
-            const uint32_t staging = smem_base + kStages * C::kStageBytes + quad * 8192;
-            epilogue_chunk_staged<OutT>(p, &tm_c, staging, lane, t.b,
-                                        t.mt * kBlockM + quad * 32, n0, bits_re, bits_im);
+            const uint32_t staging =
+                smem_base + kStages * C::kStageBytes + quad * (EPI * kStagingTile);
+            epilogue_chunk_staged<OutT, (EPI > 0 ? EPI : 2)>(p, &tm_c, staging, slot, lane, t.b,
+                                                             t.mt * kBlockM + quad * 32, n0,
+                                                             bits_re, bits_im);
             continue;
           }
         }
@@ -887,6 +893,7 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
     // ------------------------------------------------------------------ epilogue warps (both CTAs)
     const uint32_t quad = warp & 3;
     uint32_t acc = 0, acc_phase = 0;
+    uint32_t slot = 0;
     for (uint32_t tile = pair; tile < p.num_tiles; tile += num_pairs) {
       const TileCoord t = decode_tile(p, tile);
       if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, p.status,
@@ -907,7 +914,8 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         if constexpr (EPI_TMA) {
           if (p.epi_tma) {
             const uint32_t staging = smem_base + kStages * C::kStageBytes + quad * 8192;
-            epilogue_chunk_staged<OutT>(p, &tm_c, staging, lane, t.b, m0, n0, bits_re, bits_im);
+            epilogue_chunk_staged<OutT, 2>(p, &tm_c, staging, slot, lane, t.b, m0, n0, bits_re,
+                                           bits_im);
             continue;
           }
         }
@@ -999,10 +1007,11 @@ struct KernelEntry {
 
 // Four-byte outputs get the TMA-store epilogue wherever its 32 KiB of staging costs no pipeline
 // stage; that is everywhere except three A planes with 256-column tiles.
-template <int KIND, int BN, int SW, int A_PLANES, typename OutT> KernelEntry entry() {
-  constexpr bool kEpiTma = sizeof(OutT) == 4 && !(A_PLANES == 3 && BN == 256);
-  return {cgemm_tcgen05_kernel<KIND, BN, SW, A_PLANES, OutT, kEpiTma>,
-          Cfg<BN, SW, A_PLANES, kEpiTma>::kSmemBytes, kEpiTma, false};
+template <int KIND, int BN, int SW, int A_PLANES, typename OutT, int DEPTH = 2>
+KernelEntry entry() {
+  constexpr int kEpi = (sizeof(OutT) == 4 && !(A_PLANES == 3 && BN == 256)) ? DEPTH : 0;
+  return {cgemm_tcgen05_kernel<KIND, BN, SW, A_PLANES, OutT, kEpi>,
+          Cfg<BN, SW, A_PLANES, kEpi>::kSmemBytes, kEpi > 0, false};
 }
 
 template <int KIND, int BN, int A_PLANES, typename OutT, bool EPI_TMA = (sizeof(OutT) == 4)>
