@@ -1098,6 +1098,12 @@ struct ccglib_b200_gemm_plan {
   uint32_t idesc, idesc_neg_a;
   int device;
   int sms;
+  // per-plan caches: the status word's device address and the tensor maps of the last operands
+  mutable unsigned int *status_ptr;
+  mutable const void *map_a, *map_b;
+  mutable void *map_c;
+  mutable size_t map_nb;
+  mutable CUtensorMap tm_a, tm_b, tm_c;
 };
 
 extern "C" int ccglib_b200_gemm_dims(int type_in, int type_out, int variant, unsigned dims[3]) {
@@ -1408,8 +1414,10 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
   }
   p.num_tiles = static_cast<uint32_t>(tiles);
   p.tiled = tiled ? 1u : 0u;
-  CUtensorMap tm_a, tm_b;
-  int rc;
+  CUtensorMap &tm_a = plan.tm_a, &tm_b = plan.tm_b, &tm_c = plan.tm_c;
+  const bool maps_cached = plan.map_a == a && plan.map_b == b && plan.map_c == c &&
+                           plan.map_nb == nb && a != nullptr;
+  int rc = CCGLIB_B200_OK;
   if (tiled) {
     const size_t slabs_k = ceil_div<size_t>(plan.k_bytes, kSlabRowBytes);
     const size_t slabs_m = ceil_div<size_t>(d.m, kSlabRowsA);
@@ -1420,20 +1428,20 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
     p.b_slabs_n = static_cast<uint32_t>(slabs_n);
     p.b_slab_rows = kSlabRowsB;
     p.k_blocks = static_cast<uint32_t>(slabs_k * p.k_per_slab);
-    rc = make_map(&tm_a, a, kSlabRowBytes, kSlabRowsA, 2 * nb * slabs_m * slabs_k, kSlabRowBytes,
+    if (!maps_cached) rc = make_map(&tm_a, a, kSlabRowBytes, kSlabRowsA, 2 * nb * slabs_m * slabs_k, kSlabRowBytes,
                   kSlabRowBytes * kSlabRowsA, plan.sw, kBlockM, 2);
-    if (rc != CCGLIB_B200_OK) return rc;
-    rc = make_map(&tm_b, b, kSlabRowBytes, kSlabRowsB, 2 * nb * slabs_n * slabs_k, kSlabRowBytes,
+    if (!maps_cached && rc != CCGLIB_B200_OK) return rc;
+    if (!maps_cached) rc = make_map(&tm_b, b, kSlabRowBytes, kSlabRowsB, 2 * nb * slabs_n * slabs_k, kSlabRowBytes,
                   kSlabRowBytes * kSlabRowsB, plan.sw, pair ? plan.bn / 2 : plan.bn, 2);
-    if (rc != CCGLIB_B200_OK) return rc;
+    if (!maps_cached && rc != CCGLIB_B200_OK) return rc;
   } else {
     p.k_blocks = static_cast<uint32_t>(ceil_div<size_t>(plan.k_bytes, plan.sw));
-    rc = make_map(&tm_a, a, plan.k_bytes, d.m, plan.a_planes * nb, plan.pitch, plan.pitch * d.m,
+    if (!maps_cached) rc = make_map(&tm_a, a, plan.k_bytes, d.m, plan.a_planes * nb, plan.pitch, plan.pitch * d.m,
                   plan.sw, kBlockM, plan.a_planes);
-    if (rc != CCGLIB_B200_OK) return rc;
-    rc = make_map(&tm_b, b, plan.k_bytes, d.n, 2 * nb, plan.pitch, plan.pitch * d.n, plan.sw,
+    if (!maps_cached && rc != CCGLIB_B200_OK) return rc;
+    if (!maps_cached) rc = make_map(&tm_b, b, plan.k_bytes, d.n, 2 * nb, plan.pitch, plan.pitch * d.n, plan.sw,
                   pair ? plan.bn / 2 : plan.bn, 2);
-    if (rc != CCGLIB_B200_OK) return rc;
+    if (!maps_cached && rc != CCGLIB_B200_OK) return rc;
   }
   p.idesc = plan.idesc;
   p.idesc_neg_a = plan.idesc_neg_a;
@@ -1457,15 +1465,25 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
   // 512, batch 4096) distances 3..24 were 12-34 % slower than none, and slower on the others too
   p.prefetch = static_cast<uint32_t>(env_int("CCGLIB_B200_PREFETCH", 0));
   // TMA-store epilogue: row-major planar C with four-byte elements, 16-byte aligned rows
-  CUtensorMap tm_c = tm_a;  // placeholder when the epilogue stores straight from registers
   p.epi_tma = (plan.kernel.epi_tma && planar && p.vec_ok && plan.out_elem_bytes == 4) ? 1u : 0u;
-  if (p.epi_tma) {
-    rc = make_map(&tm_c, c, d.n * 4, d.m, 2 * nb, d.n * 4, d.m * d.n * 4, 128, 32, 1);
-    if (rc != CCGLIB_B200_OK) return rc;
+  if (!maps_cached) {
+    if (p.epi_tma) {
+      rc = make_map(&tm_c, c, d.n * 4, d.m, 2 * nb, d.n * 4, d.m * d.n * 4, 128, 32, 1);
+      if (rc != CCGLIB_B200_OK) return rc;
+    } else {
+      tm_c = tm_a;  // placeholder when the epilogue stores straight from registers
+    }
+    plan.map_a = a;
+    plan.map_b = b;
+    plan.map_c = c;
+    plan.map_nb = nb;
   }
-  if (cudaGetSymbolAddress(reinterpret_cast<void **>(&p.status), g_device_status) != cudaSuccess) {
+  if (plan.status_ptr == nullptr &&
+      cudaGetSymbolAddress(reinterpret_cast<void **>(&plan.status_ptr), g_device_status) !=
+          cudaSuccess) {
     return cuda_fail(cudaGetLastError(), "cudaGetSymbolAddress(g_device_status)");
   }
+  p.status = plan.status_ptr;
   if (pair) {
     const size_t clusters = tiles < static_cast<size_t>(plan.max_clusters)
                                 ? tiles
