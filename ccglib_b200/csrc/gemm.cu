@@ -63,7 +63,7 @@ struct GemmParams {
   void *c;
   uint32_t c_layout;
   uint32_t have_alpha, have_beta, vec_ok;
-  uint32_t epi_tma;  // stage C through shared memory and store it with TMA (row-major planar)
+  uint32_t epi_tma;  // stage C through shared memory and store it with TMA (row-major, 4-byte)
   uint32_t prefetch;  // k-blocks the producer asks L2 to fetch ahead of its own loads (0 = off)
   float alpha_re, alpha_im, beta_re, beta_im;
   unsigned int *status;
@@ -346,8 +346,9 @@ __device__ __forceinline__ void stage_row(uint32_t tile, uint32_t lane, const Ac
 }
 
 // Epilogue for 32 rows (one per lane, first row m0) and 32 columns from n0, stored through the
-// warp's staging tiles with TMA (row-major planar C with four-byte elements).  The real and the
-// imaginary tile are written side by side, made visible to the async proxy with one fence, and
+// warp's staging tiles with TMA (row-major C, planar or interleaved, four-byte elements).  The two
+// tiles of a chunk (real and imaginary plane, or the two halves of an interleaved row) are written
+// side by side, made visible to the async proxy with one fence, and
 // stored as one bulk group.  A warp rotates through DEPTH / 2 tile pairs and reuses a pair only
 // after the group issued from it has finished reading shared memory.
 template <typename OutT, int DEPTH>
@@ -368,15 +369,39 @@ __device__ __forceinline__ void epilogue_chunk_staged(const GemmParams &p, const
   ++slot;
   if (lane == 0) bulk_wait_group_read<DEPTH / 2 - 1>();
   __syncwarp();
-  stage_row<Acc>(tiles, lane, re);
-  stage_row<Acc>(tiles + kStagingTile, lane, im);
+  if (p.c_layout == kInterRow) {
+    // [m][n][2]: a row of 32 complex values is 256 bytes = two tiles of 16 (re, im) pairs
+    Acc lo[32], hi[32];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      lo[2 * j] = re[j];
+      lo[2 * j + 1] = im[j];
+      hi[2 * j] = re[16 + j];
+      hi[2 * j + 1] = im[16 + j];
+    }
+    stage_row<Acc>(tiles, lane, lo);
+    stage_row<Acc>(tiles + kStagingTile, lane, hi);
+  } else {
+    stage_row<Acc>(tiles, lane, re);
+    stage_row<Acc>(tiles + kStagingTile, lane, im);
+  }
   fence_proxy_async_smem();
   __syncwarp();
   if (lane == 0 && m0 < p.M) {
-    const int32_t x = static_cast<int32_t>(n0 * 4);  // the tensor map is byte-typed
-    tma_store_3d(tm_c, tiles, x, static_cast<int32_t>(m0), static_cast<int32_t>(2 * b));
-    tma_store_3d(tm_c, tiles + kStagingTile, x, static_cast<int32_t>(m0),
-                 static_cast<int32_t>(2 * b + 1));
+    // the tensor map is byte-typed: planar (N*4, M, 2*batch), interleaved (N*8, M, batch)
+    if (p.c_layout == kInterRow) {
+      const int32_t x = static_cast<int32_t>(n0 * 8);
+      tma_store_3d(tm_c, tiles, x, static_cast<int32_t>(m0), static_cast<int32_t>(b));
+      if (n0 + 16 < p.N) {
+        tma_store_3d(tm_c, tiles + kStagingTile, x + 128, static_cast<int32_t>(m0),
+                     static_cast<int32_t>(b));
+      }
+    } else {
+      const int32_t x = static_cast<int32_t>(n0 * 4);
+      tma_store_3d(tm_c, tiles, x, static_cast<int32_t>(m0), static_cast<int32_t>(2 * b));
+      tma_store_3d(tm_c, tiles + kStagingTile, x, static_cast<int32_t>(m0),
+                   static_cast<int32_t>(2 * b + 1));
+    }
     bulk_commit_group();
   }
 }
@@ -1464,11 +1489,13 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
   // L2 prefetch distance in k-blocks; off by default: on the HBM-bound short-K shape (256 x 2048 x
   // 512, batch 4096) distances 3..24 were 12-34 % slower than none, and slower on the others too
   p.prefetch = static_cast<uint32_t>(env_int("CCGLIB_B200_PREFETCH", 0));
-  // TMA-store epilogue: row-major planar C with four-byte elements, 16-byte aligned rows
-  p.epi_tma = (plan.kernel.epi_tma && planar && p.vec_ok && plan.out_elem_bytes == 4) ? 1u : 0u;
+  // TMA-store epilogue: row-major C (planar or interleaved), four-byte elements, 16-byte aligned rows
+  p.epi_tma = (plan.kernel.epi_tma && p.vec_ok && plan.out_elem_bytes == 4) ? 1u : 0u;
   if (!maps_cached) {
     if (p.epi_tma) {
-      rc = make_map(&tm_c, c, d.n * 4, d.m, 2 * nb, d.n * 4, d.m * d.n * 4, 128, 32, 1);
+      const size_t row_bytes = planar ? d.n * 4 : d.n * 8;
+      rc = make_map(&tm_c, c, row_bytes, d.m, planar ? 2 * nb : nb, row_bytes, d.m * row_bytes,
+                    128, 32, 1);
       if (rc != CCGLIB_B200_OK) return rc;
     } else {
       tm_c = tm_a;  // placeholder when the epilogue stores straight from registers
