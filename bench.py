@@ -53,9 +53,9 @@ WORKLOADS = {
 DEFAULT_WORKLOAD = "c2_f16_opt_8192_b64"
 
 # DRAM bytes (read + write) of one GEMM launch per batch item, from the ncu capture summarised in
-# profiles/cgemm_tcgen05_f16_opt_8192_batch2_ncu_full.md (5.96 GB for 2 items; items are walked
+# profiles/cgemm_tcgen05_f16_opt_8192_batch2_ncu_full.md (6.79 GB for 2 items; items are walked
 # one after another, so traffic grows in proportion to the batch).
-NCU_DRAM_BYTES_PER_ITEM = {"c2_f16_opt_8192_b64": 2.98e9}
+NCU_DRAM_BYTES_PER_ITEM = {"c2_f16_opt_8192_b64": 3.39e9}
 
 
 def measured_peaks() -> dict:
