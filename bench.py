@@ -252,18 +252,7 @@ class Workload:
         self.c = torch.empty((self.B, 2, self.M, self.N), dtype=out_dt, device=self.device)
         self.plan = capi.GemmPlan(self.B, self.M, self.N, self.K, self.type_in, self.type_out,
                                   variant=self.variant)
-        if self.type_in == self.ou.INT1:
-            chunks = -(-self.B // max(1, int(self._int1_chunk())))
-            self.launches_per_step += 3 * chunks - 1  # per chunk: expand A, expand B, GEMM
-
-    def _int1_chunk(self):
-        # mirrors the plan's staging: one e2m1 nibble per sample, planes (re, im) for A and B,
-        # equal batch chunks within the scratch cap
-        pitch = -(-(-(-self.K // 2)) // 16) * 16
-        per_item = (2 * self.M + 2 * self.N) * pitch
-        cap = max(1, min(self.B, (int(os.environ.get("CCGLIB_B200_SCRATCH_MB", "8192")) << 20)
-                         // per_item))
-        return -(-self.B // -(-self.B // cap))
+        self.launches_per_step += self.plan.launches - 1
 
     def hbm_bytes(self):
         n = sum(t.numel() * t.element_size() for t in (self.a_in, self.b_in, self.c))

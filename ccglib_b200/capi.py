@@ -20,6 +20,7 @@ OK, INVALID_ARGUMENT, UNSUPPORTED, CUDA_ERROR, DEVICE_TIMEOUT, OUT_OF_MEMORY = r
 EXPORTS = [
     "ccglib_b200_gemm_dims", "ccglib_b200_gemm_plan_create", "ccglib_b200_gemm_run",
     "ccglib_b200_gemm_plan_destroy", "ccglib_b200_gemm_plan_scratch_bytes",
+    "ccglib_b200_gemm_plan_launches",
     "ccglib_b200_transpose_run", "ccglib_b200_pack_run", "ccglib_b200_device_status",
     "ccglib_b200_status_string", "ccglib_b200_last_error",
     "ccglib_b200_gemm_int1_static_scratch",
@@ -69,6 +70,8 @@ def lib() -> ctypes.CDLL:
         L.ccglib_b200_gemm_plan_destroy.restype = ci
         L.ccglib_b200_gemm_plan_scratch_bytes.argtypes = [vp]
         L.ccglib_b200_gemm_plan_scratch_bytes.restype = sz
+        L.ccglib_b200_gemm_plan_launches.argtypes = [vp]
+        L.ccglib_b200_gemm_plan_launches.restype = sz
         L.ccglib_b200_gemm_int1_static_scratch.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp]
         L.ccglib_b200_gemm_int1_static_scratch.restype = ci
         L.ccglib_b200_transpose_run.argtypes = [sz, sz, sz, sz, sz, sz, ci, vp, vp, vp]
@@ -112,6 +115,11 @@ class GemmPlan:
     @property
     def scratch_bytes(self) -> int:
         return int(lib().ccglib_b200_gemm_plan_scratch_bytes(self._plan))
+
+    @property
+    def launches(self) -> int:
+        """Kernel launches one run() enqueues."""
+        return int(lib().ccglib_b200_gemm_plan_launches(self._plan))
 
     def run(self, d_a: int, d_b: int, d_c: int, stream: int = 0) -> None:
         _check(lib().ccglib_b200_gemm_run(self._plan, d_a, d_b, d_c, stream))

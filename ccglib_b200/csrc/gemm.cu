@@ -1119,6 +1119,14 @@ struct ccglib_b200_gemm_plan {
   size_t batch_chunk;     // batch items per kernel launch (== batch in direct mode)
   void *scratch_a, *scratch_b;
   size_t scratch_bytes;
+  // Staged modes with several chunks run on two lanes: lane j owns one scratch buffer and one
+  // internal stream and handles chunks j, j + 2, ...; while one lane's GEMM holds the SMs the
+  // other lane re-stages its next chunk beside it, and its GEMM's CTAs move in as the first
+  // one's drain.  lanes < 2: one buffer, everything on the caller's stream.
+  int lanes;
+  void *lane_a[2], *lane_b[2];
+  cudaStream_t lane_stream[2];
+  cudaEvent_t ev_fork, ev_join[2];
   size_t out_elem_bytes;
   uint32_t idesc, idesc_neg_a;
   int device;
@@ -1130,6 +1138,25 @@ struct ccglib_b200_gemm_plan {
   mutable size_t map_nb;
   mutable CUtensorMap tm_a, tm_b, tm_c;
 };
+
+namespace {
+
+void release_plan_resources(ccglib_b200_gemm_plan &plan) {
+  if (plan.lanes == 2) {
+    for (int j = 0; j < 2; ++j) {
+      if (plan.lane_stream[j] != nullptr) {
+        cudaStreamSynchronize(plan.lane_stream[j]);
+        cudaStreamDestroy(plan.lane_stream[j]);
+      }
+      if (plan.ev_join[j] != nullptr) cudaEventDestroy(plan.ev_join[j]);
+    }
+    if (plan.ev_fork != nullptr) cudaEventDestroy(plan.ev_fork);
+  }
+  if (plan.scratch_a != nullptr) cudaFree(plan.scratch_a);
+  plan.scratch_a = nullptr;
+}
+
+} // namespace
 
 extern "C" int ccglib_b200_gemm_dims(int type_in, int type_out, int variant, unsigned dims[3]) {
   (void)type_out;
@@ -1380,16 +1407,36 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
 
   // ---- scratch for the staged modes, processed in batch chunks of bounded size
   plan.batch_chunk = d.batch;
+  plan.lanes = 1;
   if (plan.stage_mode != kDirect) {
     const size_t per_item_a = plan.a_planes * d.m * plan.pitch;
     const size_t per_item_b = 2 * d.n * plan.pitch;
+    const size_t per_item = per_item_a + per_item_b;
     const size_t budget = static_cast<size_t>(env_int("CCGLIB_B200_SCRATCH_MB", 8192)) << 20;
-    size_t chunk = budget / (per_item_a + per_item_b);
-    if (chunk < 1) chunk = 1;
-    if (chunk > d.batch) chunk = d.batch;
-    chunk = ceil_div(d.batch, ceil_div(d.batch, chunk));  // equal chunks: no short last launch
+    // Two lanes pay when every chunk still fills the device several times over: aim at eight
+    // chunks of at least eight waves of tiles each, within half the budget per lane.
+    const size_t tiles_per_item = ceil_div<size_t>(d.m, plan.kernel.pair ? 2 * kBlockM : kBlockM) *
+                                  ceil_div<size_t>(d.n, plan.bn);
+    const size_t ctas = plan.kernel.pair ? static_cast<size_t>(plan.sms) / 2 : plan.sms;
+    size_t lane_chunk = ceil_div<size_t>(d.batch, 8);
+    const size_t waves = static_cast<size_t>(env_int("CCGLIB_B200_LANE_WAVES", 8));
+    const size_t min_items = ceil_div<size_t>(waves * ctas, tiles_per_item);
+    if (lane_chunk < min_items) lane_chunk = min_items;
+    if (lane_chunk * per_item > budget / 2) lane_chunk = budget / 2 / per_item;
+    const bool two_lanes = env_int("CCGLIB_B200_LANES", 2) >= 2 && lane_chunk >= 1 &&
+                           ceil_div<size_t>(d.batch, lane_chunk) >= 2;
+    size_t chunk;
+    if (two_lanes) {
+      chunk = ceil_div(d.batch, ceil_div(d.batch, lane_chunk));  // equal chunks
+      plan.lanes = 2;
+    } else {
+      chunk = budget / per_item;
+      if (chunk < 1) chunk = 1;
+      if (chunk > d.batch) chunk = d.batch;
+      chunk = ceil_div(d.batch, ceil_div(d.batch, chunk));  // equal chunks: no short last launch
+    }
     plan.batch_chunk = chunk;
-    plan.scratch_bytes = chunk * (per_item_a + per_item_b);
+    plan.scratch_bytes = plan.lanes * chunk * per_item;
     if (cudaMalloc(&plan.scratch_a, plan.scratch_bytes) != cudaSuccess) {
       cudaGetLastError();
       set_last_error("gemm_plan_create: could not allocate %zu bytes of staging scratch",
@@ -1397,11 +1444,28 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
       return CCGLIB_B200_OUT_OF_MEMORY;
     }
     plan.scratch_b = static_cast<char *>(plan.scratch_a) + chunk * per_item_a;
+    for (int j = 0; j < plan.lanes; ++j) {
+      plan.lane_a[j] = static_cast<char *>(plan.scratch_a) + j * chunk * per_item;
+      plan.lane_b[j] = static_cast<char *>(plan.lane_a[j]) + chunk * per_item_a;
+    }
+    if (plan.lanes == 2) {
+      cudaError_t err = cudaEventCreateWithFlags(&plan.ev_fork, cudaEventDisableTiming);
+      for (int j = 0; j < 2 && err == cudaSuccess; ++j) {
+        err = cudaStreamCreateWithFlags(&plan.lane_stream[j], cudaStreamNonBlocking);
+        if (err == cudaSuccess) {
+          err = cudaEventCreateWithFlags(&plan.ev_join[j], cudaEventDisableTiming);
+        }
+      }
+      if (err != cudaSuccess) {
+        release_plan_resources(plan);
+        return cuda_fail(err, "creating the staging lanes");
+      }
+    }
   }
 
   *out = new (std::nothrow) ccglib_b200_gemm_plan(plan);
   if (*out == nullptr) {
-    if (plan.scratch_a != nullptr) cudaFree(plan.scratch_a);
+    release_plan_resources(plan);
     return CCGLIB_B200_OUT_OF_MEMORY;
   }
   return CCGLIB_B200_OK;
@@ -1411,9 +1475,15 @@ extern "C" size_t ccglib_b200_gemm_plan_scratch_bytes(const ccglib_b200_gemm_pla
   return plan != nullptr ? plan->scratch_bytes : 0;
 }
 
+extern "C" size_t ccglib_b200_gemm_plan_launches(const ccglib_b200_gemm_plan *plan) {
+  if (plan == nullptr) return 0;
+  if (plan->stage_mode == kDirect) return 1;
+  return 3 * ceil_div<size_t>(plan->desc.batch, plan->batch_chunk);
+}
+
 extern "C" int ccglib_b200_gemm_plan_destroy(ccglib_b200_gemm_plan *plan) {
   if (plan == nullptr) return CCGLIB_B200_OK;
-  if (plan->scratch_a != nullptr) cudaFree(plan->scratch_a);
+  release_plan_resources(*plan);
   delete plan;
   return CCGLIB_B200_OK;
 }
@@ -1537,6 +1607,39 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
   return CCGLIB_B200_OK;
 }
 
+// Re-stage batch items [b0, b0 + nb) of A and B into (sa, sb) in the form the kernel reads.
+int stage_chunk(const ccglib_b200_gemm_plan &plan, const void *d_a, const void *d_b, size_t b0,
+                size_t nb, void *sa, void *sb, cudaStream_t stream) {
+  const ccglib_b200_gemm_desc &d = plan.desc;
+  const bool tiled_in = d.variant == CCGLIB_B200_OPT;
+  int rc;
+  if (plan.stage_mode == kExpandBits) {
+    const size_t words = ceil_div<size_t>(d.k, 32);
+    size_t a_item, b_item;
+    if (tiled_in) {
+      const size_t k_c_words = kSlabRowBytes / 4;
+      const size_t slabs_k = ceil_div<size_t>(words, k_c_words);
+      a_item = ceil_div<size_t>(d.m, kSlabRowsA) * slabs_k * 2 * kSlabRowsA * kSlabRowBytes;
+      b_item = ceil_div<size_t>(d.n, kSlabRowsB) * slabs_k * 2 * kSlabRowsB * kSlabRowBytes;
+    } else {
+      a_item = 2 * d.m * words * 4;
+      b_item = 2 * d.n * words * 4;
+    }
+    rc = launch_expand_bits(static_cast<const char *>(d_a) + b0 * a_item, sa, nb, d.m, d.k,
+                            plan.pitch, plan.a_planes, tiled_in, kSlabRowsA, kSlabRowBytes * 8,
+                            stream, plan.nibbles != 0);
+    if (rc != CCGLIB_B200_OK) return rc;
+    return launch_expand_bits(static_cast<const char *>(d_b) + b0 * b_item, sb, nb, d.n, d.k,
+                              plan.pitch, 2, tiled_in, kSlabRowsB, kSlabRowBytes * 8, stream,
+                              plan.nibbles != 0);
+  }
+  rc = launch_pad_rows(static_cast<const char *>(d_a) + b0 * 2 * d.m * plan.k_bytes, sa,
+                       nb * 2 * d.m, plan.k_bytes, plan.pitch, stream);
+  if (rc != CCGLIB_B200_OK) return rc;
+  return launch_pad_rows(static_cast<const char *>(d_b) + b0 * 2 * d.n * plan.k_bytes, sb,
+                         nb * 2 * d.n, plan.k_bytes, plan.pitch, stream);
+}
+
 } // namespace
 
 extern "C" int ccglib_b200_gemm_run(ccglib_b200_gemm_plan *plan, const void *d_a, const void *d_b,
@@ -1555,44 +1658,45 @@ extern "C" int ccglib_b200_gemm_run(ccglib_b200_gemm_plan *plan, const void *d_a
     }
     return launch_gemm(*plan, d_a, d_b, d_c, d.batch, tiled_in, stream);
   }
-  // Staged modes: re-stage a chunk of batch items into the plan's scratch, then multiply it.
+  // Staged modes: re-stage a chunk of batch items into scratch, then multiply it.
   const size_t c_item_bytes = 2 * d.m * d.n * plan->out_elem_bytes;
-  for (size_t b0 = 0; b0 < d.batch; b0 += plan->batch_chunk) {
-    const size_t nb = (d.batch - b0 < plan->batch_chunk) ? d.batch - b0 : plan->batch_chunk;
-    int rc;
-    if (plan->stage_mode == kExpandBits) {
-      const size_t words = ceil_div<size_t>(d.k, 32);
-      size_t a_item, b_item;
-      if (tiled_in) {
-        const size_t k_c_words = kSlabRowBytes / 4;
-        const size_t slabs_k = ceil_div<size_t>(words, k_c_words);
-        a_item = ceil_div<size_t>(d.m, kSlabRowsA) * slabs_k * 2 * kSlabRowsA * kSlabRowBytes;
-        b_item = ceil_div<size_t>(d.n, kSlabRowsB) * slabs_k * 2 * kSlabRowsB * kSlabRowBytes;
-      } else {
-        a_item = 2 * d.m * words * 4;
-        b_item = 2 * d.n * words * 4;
-      }
-      rc = launch_expand_bits(static_cast<const char *>(d_a) + b0 * a_item, plan->scratch_a, nb,
-                              d.m, d.k, plan->pitch, plan->a_planes, tiled_in, kSlabRowsA,
-                              kSlabRowBytes * 8, stream, plan->nibbles != 0);
+  if (plan->lanes < 2) {
+    for (size_t b0 = 0; b0 < d.batch; b0 += plan->batch_chunk) {
+      const size_t nb = (d.batch - b0 < plan->batch_chunk) ? d.batch - b0 : plan->batch_chunk;
+      int rc = stage_chunk(*plan, d_a, d_b, b0, nb, plan->scratch_a, plan->scratch_b, stream);
       if (rc != CCGLIB_B200_OK) return rc;
-      rc = launch_expand_bits(static_cast<const char *>(d_b) + b0 * b_item, plan->scratch_b, nb,
-                              d.n, d.k, plan->pitch, 2, tiled_in, kSlabRowsB, kSlabRowBytes * 8,
-                              stream, plan->nibbles != 0);
-      if (rc != CCGLIB_B200_OK) return rc;
-    } else {
-      rc = launch_pad_rows(static_cast<const char *>(d_a) + b0 * 2 * d.m * plan->k_bytes,
-                           plan->scratch_a, nb * 2 * d.m, plan->k_bytes, plan->pitch, stream);
-      if (rc != CCGLIB_B200_OK) return rc;
-      rc = launch_pad_rows(static_cast<const char *>(d_b) + b0 * 2 * d.n * plan->k_bytes,
-                           plan->scratch_b, nb * 2 * d.n, plan->k_bytes, plan->pitch, stream);
+      rc = launch_gemm(*plan, plan->scratch_a, plan->scratch_b,
+                       static_cast<char *>(d_c) + b0 * c_item_bytes, nb, false, stream);
       if (rc != CCGLIB_B200_OK) return rc;
     }
-    rc = launch_gemm(*plan, plan->scratch_a, plan->scratch_b,
-                     static_cast<char *>(d_c) + b0 * c_item_bytes, nb, false, stream);
-    if (rc != CCGLIB_B200_OK) return rc;
+    return CCGLIB_B200_OK;
   }
-  return CCGLIB_B200_OK;
+  // Two lanes: fork both internal streams off the caller's stream, deal the chunks out
+  // alternately, join both back.  Everything a lane does is ordered on its own stream, so its
+  // buffer is never re-staged before the GEMM that read it has finished.
+  CCGLIB_CUDA_TRY(cudaEventRecord(plan->ev_fork, stream));
+  for (int j = 0; j < 2; ++j) {
+    CCGLIB_CUDA_TRY(cudaStreamWaitEvent(plan->lane_stream[j], plan->ev_fork, 0));
+  }
+  int rc = CCGLIB_B200_OK;
+  size_t ci = 0;
+  for (size_t b0 = 0; b0 < d.batch && rc == CCGLIB_B200_OK; b0 += plan->batch_chunk, ++ci) {
+    const size_t nb = (d.batch - b0 < plan->batch_chunk) ? d.batch - b0 : plan->batch_chunk;
+    const int j = static_cast<int>(ci & 1);
+    rc = stage_chunk(*plan, d_a, d_b, b0, nb, plan->lane_a[j], plan->lane_b[j],
+                     plan->lane_stream[j]);
+    if (rc == CCGLIB_B200_OK) {
+      rc = launch_gemm(*plan, plan->lane_a[j], plan->lane_b[j],
+                       static_cast<char *>(d_c) + b0 * c_item_bytes, nb, false,
+                       plan->lane_stream[j]);
+    }
+  }
+  // join even after a failed launch, so that the caller's stream stays ordered after the lanes
+  for (int j = 0; j < 2; ++j) {
+    CCGLIB_CUDA_TRY(cudaEventRecord(plan->ev_join[j], plan->lane_stream[j]));
+    CCGLIB_CUDA_TRY(cudaStreamWaitEvent(stream, plan->ev_join[j], 0));
+  }
+  return rc;
 }
 
 extern "C" int ccglib_b200_device_status(unsigned *word) {

@@ -36,131 +36,78 @@ struct ExpandParams {
   size_t blk, kc_words, row_tiles, k_tiles;
 };
 
-__global__ void __launch_bounds__(256) expand_bits_kernel(const ExpandParams p) {
-  const size_t total = p.batch * 2 * p.rows * p.units;
-  for (size_t gid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; gid < total;
-       gid += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const size_t u = gid % p.units;
-    size_t t = gid / p.units;
-    const size_t r = t % p.rows;
-    t /= p.rows;
-    const size_t c = t & 1;
-    const size_t b = t >> 1;
-    size_t src;
-    if (p.tiled) {
-      const size_t rt = r / p.blk, rr = r - rt * p.blk;
-      const size_t kt = u / p.kc_words, uu = u - kt * p.kc_words;
-      src = ((((b * p.row_tiles + rt) * p.k_tiles + kt) * 2 + c) * p.blk + rr) * p.kc_words + uu;
-    } else {
-      src = ((b * 2 + c) * p.rows + r) * p.words + u;
-    }
-    const uint32_t w = __ldg(p.in + src);
-    const size_t bit0 = u * 32;
-    const int valid = static_cast<int>(p.k_bits - bit0 < 32 ? p.k_bits - bit0 : 32);
-    if (p.nibbles) {
-      // 32 samples -> 16 bytes: sample i in nibble i; +1 = 0x2 (e2m1 1.0), -1 = 0xA, padding = 0
-      uint32_t pos4[4], neg4[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t sign = spread_byte((w >> (8 * i)) & 0xFFu);  // bit j -> bit 4j
-        uint32_t mask = 0xFFFFFFFFu;
-        if (8 * i + 8 > valid) mask = (8 * i >= valid) ? 0u : ((1u << (4 * (valid - 8 * i))) - 1u);
-        pos4[i] = (0x22222222u | ((~sign & 0x11111111u) << 3)) & mask;
-        neg4[i] = (0x22222222u | (sign << 3)) & mask;
-      }
-      const size_t plane_bytes4 = p.rows * p.out_row_bytes;
-      int8_t *dst4 = p.out + ((b * p.planes_out + c) * p.rows + r) * p.out_row_bytes + u * 16;
-      *reinterpret_cast<uint4 *>(dst4) = make_uint4(pos4[0], pos4[1], pos4[2], pos4[3]);
-      if (c == 1 && p.planes_out == 3) {
-        *reinterpret_cast<uint4 *>(dst4 + plane_bytes4) =
-            make_uint4(neg4[0], neg4[1], neg4[2], neg4[3]);
-      }
-      continue;
-    }
-    uint32_t pos[8], neg[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint32_t y = spread_nibble((w >> (4 * i)) & 0xFu);
-      uint32_t mask = 0xFFFFFFFFu;
-      if (4 * i + 4 > valid) mask = (4 * i >= valid) ? 0u : ((1u << (8 * (valid - 4 * i))) - 1u);
-      pos[i] = (0xFFFFFFFFu - y * 0xFEu) & mask;  // 1 -> 0x01, 0 -> 0xFF
-      neg[i] = (0x01010101u + y * 0xFEu) & mask;  // 1 -> 0xFF, 0 -> 0x01
-    }
-    const size_t plane_bytes = p.rows * p.out_row_bytes;
-    int8_t *dst = p.out + ((b * p.planes_out + c) * p.rows + r) * p.out_row_bytes + u * 32;
-    const bool second = u * 32 + 16 < p.out_row_bytes;  // the row pitch is a multiple of 16
-    *reinterpret_cast<uint4 *>(dst) = make_uint4(pos[0], pos[1], pos[2], pos[3]);
-    if (second) *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(pos[4], pos[5], pos[6], pos[7]);
-    if (c == 1 && p.planes_out == 3) {
-      int8_t *dn = dst + plane_bytes;
-      *reinterpret_cast<uint4 *>(dn) = make_uint4(neg[0], neg[1], neg[2], neg[3]);
-      if (second) *reinterpret_cast<uint4 *>(dn + 16) = make_uint4(neg[4], neg[5], neg[6], neg[7]);
-    }
-  }
-}
-
-// Fast path for rows of whole 128-sample groups (K % 128 == 0): one thread expands four words
-// (one 16-byte load) into 64 bytes of nibbles or 128 bytes of signed bytes, so the index
-// arithmetic is paid once per 128 samples and every store is a full 16-byte vector.
+// A warp expands a block of 128 consecutive
+// words of one row, lane l taking words l, l + 32, l + 64, l + 96, so every load instruction reads
+// 128 contiguous bytes and every store instruction writes 512 (nibbles) or 2 x 512 (bytes)
+// contiguous bytes, and the row/plane arithmetic is paid once per 4096 samples.
 template <bool NIBBLES>
-__global__ void __launch_bounds__(256) expand_bits_vec_kernel(const ExpandParams p) {
-  const size_t units4 = p.words / 4;
-  const size_t total = p.batch * 2 * p.rows * units4;
+__global__ void __launch_bounds__(256) expand_bits_warp_kernel(const ExpandParams p) {
+  const size_t blocks_per_row = ceil_div<size_t>(p.words, 128);
+  const size_t total = p.batch * 2 * p.rows * blocks_per_row * 32;
   const size_t plane_bytes = p.rows * p.out_row_bytes;
+  const uint32_t lane = threadIdx.x & 31;
   for (size_t gid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; gid < total;
        gid += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const size_t u4 = gid % units4;
-    size_t t = gid / units4;
+    size_t t = gid >> 5;
+    const size_t blk = t % blocks_per_row;
+    t /= blocks_per_row;
     const size_t r = t % p.rows;
     t /= p.rows;
     const size_t c = t & 1;
     const size_t b = t >> 1;
-    size_t src;
-    if (p.tiled) {
-      const size_t u = u4 * 4;
-      const size_t rt = r / p.blk, rr = r - rt * p.blk;
-      const size_t kt = u / p.kc_words, uu = u - kt * p.kc_words;
-      src = ((((b * p.row_tiles + rt) * p.k_tiles + kt) * 2 + c) * p.blk + rr) * p.kc_words + uu;
-    } else {
-      src = ((b * 2 + c) * p.rows + r) * p.words + u4 * 4;
-    }
-    const uint4 w4 = __ldg(reinterpret_cast<const uint4 *>(p.in + src));
-    const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
     const bool negated_plane = c == 1 && p.planes_out == 3;
-    if constexpr (NIBBLES) {
-      uint4 *dst = reinterpret_cast<uint4 *>(
-          p.out + ((b * p.planes_out + c) * p.rows + r) * p.out_row_bytes + u4 * 64);
-      uint4 *dneg = reinterpret_cast<uint4 *>(reinterpret_cast<int8_t *>(dst) + plane_bytes);
+    int8_t *out_row = p.out + ((b * p.planes_out + c) * p.rows + r) * p.out_row_bytes;
+    const size_t rt = r / p.blk, rr = r - rt * p.blk;
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
+    for (int i = 0; i < 4; ++i) {
+      const size_t u = blk * 128 + i * 32 + lane;  // word within the row
+      if (u >= p.words) continue;
+      size_t src;
+      if (p.tiled) {
+        const size_t kt = u / p.kc_words, uu = u - kt * p.kc_words;
+        src = ((((b * p.row_tiles + rt) * p.k_tiles + kt) * 2 + c) * p.blk + rr) * p.kc_words + uu;
+      } else {
+        src = ((b * 2 + c) * p.rows + r) * p.words + u;
+      }
+      const uint32_t w = __ldg(p.in + src);
+      const size_t bit0 = u * 32;
+      const int valid = static_cast<int>(p.k_bits - bit0 < 32 ? p.k_bits - bit0 : 32);
+      if constexpr (NIBBLES) {
         uint32_t pos[4], neg[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint32_t sign = spread_byte((w[q] >> (8 * i)) & 0xFFu);
-          pos[i] = 0x22222222u | ((~sign & 0x11111111u) << 3);
-          neg[i] = 0x22222222u | (sign << 3);
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t sign = spread_byte((w >> (8 * q)) & 0xFFu);
+          uint32_t mask = 0xFFFFFFFFu;
+          if (8 * q + 8 > valid) mask = (8 * q >= valid) ? 0u : ((1u << (4 * (valid - 8 * q))) - 1u);
+          pos[q] = (0x22222222u | ((~sign & 0x11111111u) << 3)) & mask;
+          neg[q] = (0x22222222u | (sign << 3)) & mask;
         }
-        dst[q] = make_uint4(pos[0], pos[1], pos[2], pos[3]);
-        if (negated_plane) dneg[q] = make_uint4(neg[0], neg[1], neg[2], neg[3]);
-      }
-    } else {
-      uint4 *dst = reinterpret_cast<uint4 *>(
-          p.out + ((b * p.planes_out + c) * p.rows + r) * p.out_row_bytes + u4 * 128);
-      uint4 *dneg = reinterpret_cast<uint4 *>(reinterpret_cast<int8_t *>(dst) + plane_bytes);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
+        uint4 *dst = reinterpret_cast<uint4 *>(out_row + u * 16);
+        *dst = make_uint4(pos[0], pos[1], pos[2], pos[3]);
+        if (negated_plane) {
+          *reinterpret_cast<uint4 *>(reinterpret_cast<int8_t *>(dst) + plane_bytes) =
+              make_uint4(neg[0], neg[1], neg[2], neg[3]);
+        }
+      } else {
         uint32_t pos[8], neg[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const uint32_t y = spread_nibble((w[q] >> (4 * i)) & 0xFu);
-          pos[i] = 0xFFFFFFFFu - y * 0xFEu;
-          neg[i] = 0x01010101u + y * 0xFEu;
+        for (int q = 0; q < 8; ++q) {
+          const uint32_t y = spread_nibble((w >> (4 * q)) & 0xFu);
+          uint32_t mask = 0xFFFFFFFFu;
+          if (4 * q + 4 > valid) mask = (4 * q >= valid) ? 0u : ((1u << (8 * (valid - 4 * q))) - 1u);
+          pos[q] = (0xFFFFFFFFu - y * 0xFEu) & mask;
+          neg[q] = (0x01010101u + y * 0xFEu) & mask;
         }
-        dst[2 * q] = make_uint4(pos[0], pos[1], pos[2], pos[3]);
-        dst[2 * q + 1] = make_uint4(pos[4], pos[5], pos[6], pos[7]);
+        int8_t *dst = out_row + u * 32;
+        const bool second = u * 32 + 16 < p.out_row_bytes;
+        *reinterpret_cast<uint4 *>(dst) = make_uint4(pos[0], pos[1], pos[2], pos[3]);
+        if (second) *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(pos[4], pos[5], pos[6], pos[7]);
         if (negated_plane) {
-          dneg[2 * q] = make_uint4(neg[0], neg[1], neg[2], neg[3]);
-          dneg[2 * q + 1] = make_uint4(neg[4], neg[5], neg[6], neg[7]);
+          int8_t *dn = dst + plane_bytes;
+          *reinterpret_cast<uint4 *>(dn) = make_uint4(neg[0], neg[1], neg[2], neg[3]);
+          if (second) {
+            *reinterpret_cast<uint4 *>(dn + 16) = make_uint4(neg[4], neg[5], neg[6], neg[7]);
+          }
         }
       }
     }
@@ -213,21 +160,16 @@ int launch_expand_bits(const void *d_in, void *d_out, size_t batch, size_t rows,
   p.kc_words = k_c_bits / 32;
   p.row_tiles = ceil_div<size_t>(rows, blk);
   p.k_tiles = ceil_div<size_t>(p.words, p.kc_words);
-  const bool vec = k_bits % 128 == 0 && aligned16(d_in) && (!tiled || p.kc_words % 4 == 0);
-  if (vec) {
-    const size_t total4 = batch * 2 * rows * (p.words / 4);
+  {
+    const size_t total_w = batch * 2 * rows * ceil_div<size_t>(p.words, 128) * 32;
     if (nibbles) {
-      expand_bits_vec_kernel<true><<<grid_for(total4, 256), 256, 0, stream>>>(p);
+      expand_bits_warp_kernel<true><<<grid_for(total_w, 256), 256, 0, stream>>>(p);
     } else {
-      expand_bits_vec_kernel<false><<<grid_for(total4, 256), 256, 0, stream>>>(p);
+      expand_bits_warp_kernel<false><<<grid_for(total_w, 256), 256, 0, stream>>>(p);
     }
     CCGLIB_CUDA_TRY(cudaGetLastError());
     return CCGLIB_B200_OK;
   }
-  const size_t total = batch * 2 * rows * p.units;
-  expand_bits_kernel<<<grid_for(total, 256), 256, 0, stream>>>(p);
-  CCGLIB_CUDA_TRY(cudaGetLastError());
-  return CCGLIB_B200_OK;
 }
 
 int launch_pad_rows(const void *d_in, void *d_out, size_t rows, size_t row_bytes,

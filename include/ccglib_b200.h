@@ -109,6 +109,11 @@ CCGLIB_B200_API int ccglib_b200_gemm_plan_destroy(ccglib_b200_gemm_plan *plan);
 /* Bytes of device scratch the plan owns (0 for the direct TMA path). */
 CCGLIB_B200_API size_t ccglib_b200_gemm_plan_scratch_bytes(const ccglib_b200_gemm_plan *plan);
 
+/* Kernel launches one ccglib_b200_gemm_run of this plan enqueues: 1 on the direct TMA path,
+ * 3 per batch chunk (re-stage A, re-stage B, multiply) on the staged paths.  Introspection for
+ * benchmarks; no counterpart in the reference. */
+CCGLIB_B200_API size_t ccglib_b200_gemm_plan_launches(const ccglib_b200_gemm_plan *plan);
+
 /*
  * Tile transpose: [batch][2][M][N] (planar) or [batch][M][N][2] (interleaved) ->
  * [batch][ceil(M/m_chunk)][ceil(N/n_chunk)][2][m_chunk][n_chunk], zero padded.  Elements are

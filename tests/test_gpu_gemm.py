@@ -328,6 +328,38 @@ def test_staged_batch_chunks(monkeypatch):
     assert np.array_equal(got, gu.oracle_batch(ou.INT1, ou.INT32, a, b, B, M, N, K))
 
 
+@pytest.mark.parametrize("type_in,type_out,K", [(ou.INT1, ou.INT32, 1056), (ou.F16, ou.F32, 100)])
+def test_staged_two_lanes(monkeypatch, type_in, type_out, K):
+    """Staged plans with several chunks alternate them over two internal streams; the result must
+    equal the single-lane one bit for bit, run after run, and match the oracle."""
+    import torch
+
+    B, M, N = 7, 200, 264
+    a, b = make_inputs(31, type_in, B, M, N, K)
+    d_a, d_b = gu.dev(a), gu.dev(b)
+    outs = []
+    for lanes in ("1", "2"):
+        monkeypatch.setenv("CCGLIB_B200_LANES", lanes)
+        monkeypatch.setenv("CCGLIB_B200_LANE_WAVES", "0")  # small chunks qualify
+        plan = capi.GemmPlan(B, M, N, K, type_in, type_out, variant=capi.BASIC)
+        assert plan.launches == (3 * 7 if lanes == "2" else 3)
+        for _ in range(2):
+            d_c = gu.dev_empty(B * 2 * M * N * 4, 0xFF)
+            plan.run(d_a.data_ptr(), d_b.data_ptr(), d_c.data_ptr(), gu.stream_handle())
+            torch.cuda.synchronize()
+            gu.check_device_status()
+            outs.append(d_c)
+        plan.close()
+    for other in outs[1:]:
+        assert torch.equal(outs[0], other)
+    dt = np.int32 if type_out == ou.INT32 else np.float32
+    got = gu.host(outs[-1], dt).reshape(B, 2, M, N)
+    if type_in == ou.INT1:
+        assert np.array_equal(got, gu.oracle_batch(type_in, type_out, a, b, B, M, N, K))
+    else:
+        gu.assert_close_fp64(got, type_in, type_out, a, b, K)
+
+
 def test_run_twice_same_plan_is_deterministic():
     import torch
 
