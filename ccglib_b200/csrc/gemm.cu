@@ -1312,9 +1312,18 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
 
   // ---- tile shape
   // BN = 256 halves the shared-memory traffic per flop; BN = 128 double-buffers the accumulators
-  // so the epilogue overlaps the next tile's main loop (short K) and gives more tiles (small M*N).
-  const size_t tiles_256 = d.batch * ceil_div<size_t>(d.m, kBlockM) * ceil_div<size_t>(d.n, 256);
-  int bn = (plan.k_bytes <= 2048 || tiles_256 < static_cast<size_t>(plan.sms)) ? 128 : 256;
+  // so the epilogue overlaps the next tile's main loop (short K), wastes less on a ragged N and
+  // gives more tiles (small M*N).  Compare waves of tiles x relative time per tile; the two
+  // efficiency factors are measured: at 2 KB rows the 256-wide tile is 5-8 % slower per flop, at
+  // 4 KB rows and beyond 3-7 % faster.
+  const size_t tiles_m = d.batch * ceil_div<size_t>(d.m, kBlockM);
+  const size_t sms = static_cast<size_t>(plan.sms);
+  const bool short_k = plan.k_bytes <= 2048;
+  const double cost_128 = static_cast<double>(ceil_div(tiles_m * ceil_div<size_t>(d.n, 128), sms)) *
+                          (short_k ? 1.0 : 1.05);
+  const double cost_256 = static_cast<double>(ceil_div(tiles_m * ceil_div<size_t>(d.n, 256), sms)) *
+                          2.0 * (short_k ? 1.06 : 1.0);
+  int bn = cost_256 <= cost_128 ? 256 : 128;
   int sw = 128;
   bn = env_int("CCGLIB_B200_BN", bn);
   sw = env_int("CCGLIB_B200_SW", sw);
