@@ -103,6 +103,7 @@ KernelEntry pick_tile(int bn, int sw, bool pair = false) {
     return sw == 128 ? entry<KIND, 256, 128, A_PLANES, OutT>()
                      : entry<KIND, 256, 64, A_PLANES, OutT>();
   }
+  if (bn == 64) return entry<KIND, 64, 128, A_PLANES, OutT>();
   return sw == 128 ? entry<KIND, 128, 128, A_PLANES, OutT>()
                    : entry<KIND, 128, 64, A_PLANES, OutT>();
 }
@@ -142,6 +143,11 @@ size_t type_bits(int t) {
     return 0;
   }
 }
+
+// Time per flop of a 64-column tile relative to 128 columns: an N = 64 MMA takes as long as an
+// N = 128 one (measured 823 against 1537 TFLOP/s on full waves), so the narrow tile only pays
+// when it turns idle SMs into a shorter single wave.
+constexpr double kCost64 = 1.9;
 
 constexpr unsigned kSlabRowBytes = 128;  // bytes per slab row of the opt layout
 constexpr unsigned kSlabRowsA = 128;     // m_blk
@@ -371,28 +377,35 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
                           (short_k ? 1.0 : 1.05);
   const double cost_256 = static_cast<double>(ceil_div(tiles_m * ceil_div<size_t>(d.n, 256), sms)) *
                           2.0 * (short_k ? 1.06 : 1.0);
+  // 64-column tiles double the tile count once more for problems that cannot fill the SMs (a
+  // single 1024^3 product is 64 tiles of 128 x 128: 466 against 419 TFLOP/s).
+  const double cost_64 = static_cast<double>(ceil_div(tiles_m * ceil_div<size_t>(d.n, 64), sms)) *
+                         0.5 * kCost64;
   int bn = cost_256 <= cost_128 ? 256 : 128;
+  if (cost_64 < (bn == 256 ? cost_256 : cost_128)) bn = 64;
   int sw = 128;
   bn = env_int("CCGLIB_B200_BN", bn);
   sw = env_int("CCGLIB_B200_SW", sw);
   if (kind == kKindMXF4) {
     // two accumulators plus the scale-factor columns must fit 512 tensor-memory columns
     if (bn == 256) bn = 192;
+    if (bn == 64) bn = 128;
     sw = 128;
   }
-  if ((bn != 128 && bn != 256 && !(bn == 192 && kind == kKindMXF4)) || (sw != 64 && sw != 128)) {
-    set_last_error("CCGLIB_B200_BN must be 128 or 256 and CCGLIB_B200_SW 64 or 128");
+  if (bn == 64) sw = 128;
+  if ((bn != 64 && bn != 128 && bn != 256 && !(bn == 192 && kind == kKindMXF4)) || (sw != 64 && sw != 128)) {
+    set_last_error("CCGLIB_B200_BN must be 64, 128 or 256 and CCGLIB_B200_SW 64 or 128");
     return CCGLIB_B200_INVALID_ARGUMENT;
   }
   // CTA pairs (cta_group::2, 256-row tiles) are opt-in: they reach a higher tensor-pipe duty cycle
-  // per clock (95.8 % against 86 % on 8192^3 f16) but draw more power per flop (half of B comes
-  // over the SM-to-SM network), so under the 1 kW cap the clock falls further than the duty
-  // cycle rises (990 against 1312 MHz; 1150 against 1369 TFLOP/s), and in short, clock-unlimited
-  // runs they were 1-9 % slower as well.
+  // per clock (95.8 % against 91.8 % on 8192^3 f16) and win a 0.3 s burst (2084 against 1816
+  // TFLOP/s), but every MMA reads half of B over the SM-to-SM network, twice per k-step in the
+  // four-product complex scheme, which costs about 20 % more energy per flop: in runs of seconds
+  // the 1 kW cap pulls the clock to 1.0 GHz against 1.25 GHz (1116 against 1341 TFLOP/s).
   // The 4-bit path is the exception: it is bound by operand traffic from L2, not by power, and a
   // pair halves the B bytes each SM fetches (5.6 against 5.3 POPS at 4096 x 4096 x 65536).
   const bool pair = env_int("CCGLIB_B200_PAIR", kind == kKindMXF4 ? 1 : 0) != 0 && sw == 128 &&
-                    d.m > kBlockM;
+                    bn != 64 && d.m > kBlockM;
   plan.bn = bn;
   plan.sw = sw;
   switch (kind) {

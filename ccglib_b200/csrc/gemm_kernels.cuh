@@ -82,7 +82,7 @@ template <int BN, int SW, int A_PLANES, int EPI> struct Cfg {
   static constexpr int kStaging = 4 * EPI * kStagingTile;  // EPI tiles per epilogue warp
   static constexpr int kStagesRaw = (kMaxSmem - 1024 - kBarrierBytes - kStaging) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kAccStages = (BN == 128) ? 2 : 1;
+  static constexpr int kAccStages = (BN <= 128) ? 2 : 1;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStaging + 1024 + kBarrierBytes;
   static_assert(kStages >= 2, "need at least two stages");
   static_assert(2 * BN * kAccStages <= kTmemCols, "accumulators exceed tensor memory");
