@@ -47,5 +47,27 @@ def build(force: bool = False) -> str:
     return BIN
 
 
+REFERENCE_CLASS_LIB = os.path.join(HERE, "bin", "libreference_class.so")
+
+
+def build_reference_class(force: bool = False) -> str:
+    """C entry points (oracle/ref_wrap.cpp, the ones the tests already use for the reference's own
+    CPU GEMM) compiled against THIS repository's include/ccglib/gemm/reference.h, so that the
+    header-only ccglib::reference::GEMM can be called from Python.  Host only: no CUDA library."""
+    wrap = os.path.join(ROOT, "oracle", "ref_wrap.cpp")
+    header = os.path.join(ROOT, "include", "ccglib", "gemm", "reference.h")
+    deps = [wrap, header, os.path.join(ROOT, "include", "ccglib", "b200_api.hpp"), __file__]
+    if not force and os.path.exists(REFERENCE_CLASS_LIB) and all(
+            os.path.getmtime(d) <= os.path.getmtime(REFERENCE_CLASS_LIB) for d in deps):
+        return REFERENCE_CLASS_LIB
+    os.makedirs(os.path.dirname(REFERENCE_CLASS_LIB), exist_ok=True)
+    cmd = ["g++", "-std=c++17", "-O2", "-ffp-contract=off", "-fopenmp", "-fPIC", "-shared", "-Wall",
+           "-I", os.path.join(ROOT, "include"), "-I", os.path.join(CUDA_HOME, "include"),
+           "-o", REFERENCE_CLASS_LIB, wrap]
+    subprocess.run(cmd, check=True)
+    return REFERENCE_CLASS_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv))
+    print(build_reference_class(force="--force" in sys.argv))

@@ -75,15 +75,19 @@ def load_reference():
         if path is None or not os.path.exists(path):
             _ref = None
         else:
-            lib = ctypes.CDLL(path)
-            for name in ("e4m3_f32", "e5m2_f32", "f16_f16", "f16_f32", "f32_f16", "bf16_bf16",
-                         "bf16_f32", "f32_bf16", "f32_f32", "int1_s32"):
-                fn = getattr(lib, "ref_gemm_" + name)
-                fn.argtypes = [_vp, _vp, _vp, _c_size_t, _c_size_t, _c_size_t, _c_int, _c_float,
-                               _c_float, _c_float, _c_float]
-                fn.restype = None
-            _ref = lib
+            _ref = bind_reference_entry_points(ctypes.CDLL(path))
     return _ref
+
+
+def bind_reference_entry_points(lib):
+    """ctypes prototypes of the ten ref_gemm_* entry points of oracle/ref_wrap.cpp."""
+    for name in ("e4m3_f32", "e5m2_f32", "f16_f16", "f16_f32", "f32_f16", "bf16_bf16",
+                 "bf16_f32", "f32_bf16", "f32_f32", "int1_s32"):
+        fn = getattr(lib, "ref_gemm_" + name)
+        fn.argtypes = [_vp, _vp, _vp, _c_size_t, _c_size_t, _c_size_t, _c_int, _c_float,
+                       _c_float, _c_float, _c_float]
+        fn.restype = None
+    return lib
 
 
 # --------------------------------------------------------------------------- conversions
