@@ -8,8 +8,11 @@ runs with the operands resident on the device.
     python -m ccglib_b200.benchmark transpose --b 8 --m 8192 --n 8192 --precision float16
     python -m ccglib_b200.benchmark packing --n 1073741824 --direction pack
 
-Several sizes may be given (`--m 1024,2048 --n ... --k ...`).  torch only provides device memory,
-streams and events; the work goes through the C ABI.
+Several sizes may be given (`--m 1024,2048 --n ... --k ...`).  `--pad` rounds M, N, K up to the
+tile sizes of `GetDimensions`, as the reference's flag does.  `--measure_power` adds the average
+board power over the timed runs and TOps/J (the reference reads a PMT sensor,
+benchmark_gemm.cpp:239-243,279-320; here the difference of NVML's total-energy counter, a read-only
+query).  torch only provides device memory, streams and events; the work goes through the C ABI.
 """
 from __future__ import annotations
 
@@ -29,8 +32,28 @@ def _sizes(text: str) -> list[int]:
     return [int(x) for x in text.split(",") if x]
 
 
-def _time(fn, duration_s: float, warm: bool):
-    """(ms per run, runs): the reference's scheme with CUDA events."""
+class _EnergyMeter:
+    """Joules drawn by one GPU between start() and stop(), from NVML's millijoule counter."""
+
+    def __init__(self, device_index: int):
+        import pynvml
+        import torch
+
+        pynvml.nvmlInit()
+        self._nvml = pynvml
+        # torch's ordinal follows CUDA_VISIBLE_DEVICES; NVML's does not: go through the UUID
+        uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+        self._handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+
+    def start(self) -> None:
+        self._mj = self._nvml.nvmlDeviceGetTotalEnergyConsumption(self._handle)
+
+    def stop(self) -> float:
+        return (self._nvml.nvmlDeviceGetTotalEnergyConsumption(self._handle) - self._mj) * 1e-3
+
+
+def _time(fn, duration_s: float, warm: bool, meter: "_EnergyMeter | None" = None):
+    """(ms per run, runs, watts or None): the reference's scheme with CUDA events."""
     import torch
 
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -43,15 +66,21 @@ def _time(fn, duration_s: float, warm: bool):
         for _ in range(iterations):
             fn()
     torch.cuda.synchronize()
+    if meter is not None:
+        meter.start()
     start.record()
     for _ in range(iterations):
         fn()
     end.record()
     torch.cuda.synchronize()
+    joules = meter.stop() if meter is not None else None
     status = capi.device_status()
     if status:
         raise RuntimeError("device status word 0x%x" % status)
-    return start.elapsed_time(end) / iterations, iterations
+    total_ms = start.elapsed_time(end)
+    # NVML refreshes the counter every few tens of milliseconds: a shorter run reads 0 J -> nan
+    watts = None if joules is None else (joules / (1e-3 * total_ms) if joules > 0 else float("nan"))
+    return total_ms / iterations, iterations, watts
 
 
 def _ceil(a: int, b: int) -> int:
@@ -69,11 +98,14 @@ def bench_gemm(args) -> None:
     axis = capi.INTERLEAVED if args.complex_axis == "interleaved" else capi.PLANAR
     m_blk, n_blk, k_c = capi.gemm_dims(tin, tout, variant)
     stream = int(torch.cuda.current_stream().cuda_stream)
+    meter = _EnergyMeter(args.device) if args.measure_power else None
     if args.csv:
-        print("#M,N,K,runtime_ms,tops")
+        print("#M,N,K,runtime_ms,tops" + (",watt,tops_per_joule" if meter else ""))
     first = True
     for _ in range(args.nr_benchmarks):
         for M, N, K in zip(_sizes(args.m), _sizes(args.n), _sizes(args.k)):
+            if args.pad:
+                M, N, K = _ceil(M, m_blk) * m_blk, _ceil(N, n_blk) * n_blk, _ceil(K, k_c) * k_c
             if variant == capi.OPT:  # zero-padded tiled operands
                 a_bytes = args.b * 2 * _ceil(M, m_blk) * m_blk * _ceil(K, k_c) * k_c * BITS[tin] // 8
                 b_bytes = args.b * 2 * _ceil(N, n_blk) * n_blk * _ceil(K, k_c) * k_c * BITS[tin] // 8
@@ -85,14 +117,17 @@ def bench_gemm(args) -> None:
             d_b = torch.full((b_bytes,), 0x3C, dtype=torch.uint8, device="cuda")
             d_c = torch.empty(args.b * 2 * M * N * BITS[tout] // 8, dtype=torch.uint8, device="cuda")
             plan = capi.GemmPlan(args.b, M, N, K, tin, tout, variant=variant, c_complex_axis=axis)
-            ms, _ = _time(lambda: plan.run(d_a.data_ptr(), d_b.data_ptr(), d_c.data_ptr(), stream),
-                          args.benchmark_duration, first)
+            ms, _, watts = _time(
+                lambda: plan.run(d_a.data_ptr(), d_b.data_ptr(), d_c.data_ptr(), stream),
+                args.benchmark_duration, first, meter)
             first = False
             tops = 8e-9 * args.b * M * N * K / ms
             if args.csv:
-                print("%d,%d,%d,%g,%g" % (M, N, K, ms, tops))
+                print("%d,%d,%d,%g,%g" % (M, N, K, ms, tops) +
+                      (",%g,%g" % (watts, tops / watts) if meter else ""))
             else:
-                print("%20s %7.4g ms, %7.4g TOps/s" % ("%dx%dx%d" % (M, N, K), ms, tops))
+                print("%20s %7.4g ms, %7.4g TOps/s" % ("%dx%dx%d" % (M, N, K), ms, tops) +
+                      (", %7.4g W, %7.4g TOps/J" % (watts, tops / watts) if meter else ""))
             plan.close()
             del d_a, d_b, d_c
 
@@ -107,8 +142,9 @@ def bench_transpose(args) -> None:
     axis = capi.INTERLEAVED if args.complex_axis == "interleaved" else capi.PLANAR
     m_blk, _, k_c = capi.gemm_dims(t, tout, variant)
     stream = int(torch.cuda.current_stream().cuda_stream)
+    meter = _EnergyMeter(args.device) if args.measure_power else None
     if args.csv:
-        print("#M,N,runtime_ms,gbytes_per_s")
+        print("#M,N,runtime_ms,gbytes_per_s" + (",watt" if meter else ""))
     first = True
     for _ in range(args.nr_benchmarks):
         for M, N in zip(_sizes(args.m), _sizes(args.n)):
@@ -116,15 +152,16 @@ def bench_transpose(args) -> None:
             out_bytes = args.b * 2 * _ceil(M, m_blk) * m_blk * _ceil(N, k_c) * k_c * bits // 8
             d_in = torch.full((in_bytes,), 0x3C, dtype=torch.uint8, device="cuda")
             d_out = torch.empty(out_bytes, dtype=torch.uint8, device="cuda")
-            ms, _ = _time(lambda: capi.transpose(args.b, M, N, m_blk, k_c, bits, axis,
-                                                 d_in.data_ptr(), d_out.data_ptr(), stream),
-                          args.benchmark_duration, first)
+            ms, _, watts = _time(lambda: capi.transpose(args.b, M, N, m_blk, k_c, bits, axis,
+                                                        d_in.data_ptr(), d_out.data_ptr(), stream),
+                                 args.benchmark_duration, first, meter)
             first = False
             gbs = 2e-6 * in_bytes / ms  # bytes read + bytes written, padding not counted
             if args.csv:
-                print("%d,%d,%g,%g" % (M, N, ms, gbs))
+                print("%d,%d,%g,%g" % (M, N, ms, gbs) + (",%g" % watts if meter else ""))
             else:
-                print("%20s %7.4g ms, %7.4g GByte/s" % ("%dx%d" % (M, N), ms, gbs))
+                print("%20s %7.4g ms, %7.4g GByte/s" % ("%dx%d" % (M, N), ms, gbs) +
+                      (", %7.4g W" % watts if meter else ""))
             del d_in, d_out
 
 
@@ -133,8 +170,9 @@ def bench_packing(args) -> None:
 
     direction = capi.FORWARD if args.direction == "pack" else capi.BACKWARD
     stream = int(torch.cuda.current_stream().cuda_stream)
+    meter = _EnergyMeter(args.device) if args.measure_power else None
     if args.csv:
-        print("#N,runtime_ms,gbytes_per_s")
+        print("#N,runtime_ms,gbytes_per_s" + (",watt" if meter else ""))
     first = True
     for _ in range(args.nr_benchmarks):
         for N in _sizes(args.n):
@@ -142,15 +180,16 @@ def bench_packing(args) -> None:
             word_side = torch.zeros(_ceil(N, 32) * 4, dtype=torch.uint8, device="cuda")
             src, dst = (byte_side, word_side) if direction == capi.FORWARD else (word_side,
                                                                                byte_side)
-            ms, _ = _time(lambda: capi.pack(N, direction, capi.PLANAR, src.data_ptr(),
-                                            dst.data_ptr(), stream),
-                          args.benchmark_duration, first)
+            ms, _, watts = _time(lambda: capi.pack(N, direction, capi.PLANAR, src.data_ptr(),
+                                                   dst.data_ptr(), stream),
+                                 args.benchmark_duration, first, meter)
             first = False
             gbs = 1e-6 * (N + N / 8) / ms
             if args.csv:
-                print("%d,%g,%g" % (N, ms, gbs))
+                print("%d,%g,%g" % (N, ms, gbs) + (",%g" % watts if meter else ""))
             else:
-                print("%20d %7.4g ms, %7.4g GByte/s" % (N, ms, gbs))
+                print("%20d %7.4g ms, %7.4g GByte/s" % (N, ms, gbs) +
+                      (", %7.4g W" % watts if meter else ""))
             del byte_side, word_side
 
 
@@ -163,12 +202,14 @@ def main(argv=None) -> int:
         p.add_argument("--benchmark_duration", type=float, default=4.0)
         p.add_argument("--csv", action="store_true")
         p.add_argument("--device", type=int, default=0)
+        p.add_argument("--measure_power", action="store_true")
 
     g = sub.add_parser("gemm")
     g.add_argument("--b", type=int, default=1)
     g.add_argument("--m", required=True)
     g.add_argument("--n", required=True)
     g.add_argument("--k", required=True)
+    g.add_argument("--pad", action="store_true")
     g.add_argument("--precision_in", default="float32", choices=sorted(PRECISIONS))
     g.add_argument("--precision_out", default="float32", choices=sorted(PRECISIONS))
     g.add_argument("--variant", default="opt", choices=["basic", "opt"])

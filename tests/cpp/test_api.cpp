@@ -18,6 +18,7 @@
 #include <cudawrappers/cu.hpp>
 
 #include <ccglib/ccglib.hpp>
+#include <ccglib/common/arch.h>
 #include <ccglib/fp16.h>
 
 extern "C" {
@@ -311,6 +312,19 @@ bool error_cases(Cuda &cuda) {
   const dim3 dims = ccglib::mma::GEMM::GetDimensions(ccglib::ValueType::float16);
   ok = ok && dims.x == 128 && dims.y == 256 && dims.z == 64;
   ok = ok && ccglib::helper::ceildiv(10, 3) == 4 && ccglib::helper::ceildiv(9, 3) == 3;
+  // the architecture predicates reference tests skip on (test/gemm/mma.cpp:530-591)
+  {
+    cu::Device device(0);
+    ok = ok && ccglib::isBlackwell(device.getArch()) && ccglib::hasFP8(device) &&
+         !ccglib::isVolta(device) && !ccglib::isCDNA(device) && !ccglib::isUnsupported(device);
+  }
+  // the CPU verification class is part of the umbrella header
+  {
+    const float a[4] = {1, 2, 3, 4}, b[4] = {5, 6, 7, 8};  // [2][1][2] each
+    float c[2] = {0, 0};
+    ccglib::reference::GEMM().Run(a, b, c, 1, 1, 2);
+    ok = ok && c[0] == (1 * 5 + 2 * 6) - (3 * 7 + 4 * 8) && c[1] == (1 * 7 + 2 * 8) + (3 * 5 + 4 * 6);
+  }
   return ok;
 }
 

@@ -10,9 +10,9 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(*args):
+def _run(*args, duration="0.05"):
     res = subprocess.run([sys.executable, "-m", "ccglib_b200.benchmark", *args, "--csv",
-                          "--benchmark_duration", "0.05"], cwd=ROOT, capture_output=True,
+                          "--benchmark_duration", duration], cwd=ROOT, capture_output=True,
                          text=True, timeout=300)
     assert res.returncode == 0, res.stderr
     lines = res.stdout.strip().splitlines()
@@ -37,3 +37,14 @@ def test_transpose_and_packing_cli():
     for direction in ("pack", "unpack"):
         header, rows = _run("packing", "--n", str(1 << 22), "--direction", direction)
         assert header == "#N,runtime_ms,gbytes_per_s" and float(rows[0][2]) > 0
+
+
+def test_gemm_cli_pad_and_power():
+    """--pad rounds the sizes up to the GetDimensions tile (128, 256, 64 for float16);
+    --measure_power appends the reference's two extra columns."""
+    header, rows = _run("gemm", "--b", "4", "--m", "1000", "--n", "1000", "--k", "1000",
+                        "--precision_in", "float16", "--pad", "--measure_power", duration="1.0")
+    assert header == "#M,N,K,runtime_ms,tops,watt,tops_per_joule"
+    assert rows[0][:3] == ["1024", "1024", "1024"]
+    watts, tops_per_joule = float(rows[0][5]), float(rows[0][6])
+    assert 10 < watts < 1500 and tops_per_joule > 0
