@@ -398,10 +398,11 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
     return CCGLIB_B200_INVALID_ARGUMENT;
   }
   // CTA pairs (cta_group::2, 256-row tiles) are opt-in: they reach a higher tensor-pipe duty cycle
-  // per clock (95.8 % against 91.8 % on 8192^3 f16) and win a 0.3 s burst (2084 against 1816
-  // TFLOP/s), but every MMA reads half of B over the SM-to-SM network, twice per k-step in the
-  // four-product complex scheme, which costs about 20 % more energy per flop: in runs of seconds
-  // the 1 kW cap pulls the clock to 1.0 GHz against 1.25 GHz (1116 against 1341 TFLOP/s).
+  // per clock (95.8 % against 91.8 % on 8192^3 f16), but every MMA reads half of B over the
+  // SM-to-SM network, twice per k-step in the four-product complex scheme, which costs about 20 %
+  // more energy per flop.  While the 1 kW cap does not bind (constant operand bytes) the pair is
+  // 1-8 % ahead; on normally distributed operands the cap pulls its clock to 1.0 GHz against
+  // 1.25 GHz and it delivers 1116 against 1341 TFLOP/s.
   // The 4-bit path is the exception: it is bound by operand traffic from L2, not by power, and a
   // pair halves the B bytes each SM fetches (5.6 against 5.3 POPS at 4096 x 4096 x 65536).
   const bool pair = env_int("CCGLIB_B200_PAIR", kind == kKindMXF4 ? 1 : 0) != 0 && sw == 128 &&
