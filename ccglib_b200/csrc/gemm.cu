@@ -386,14 +386,20 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
   int sw = 128;
   bn = env_int("CCGLIB_B200_BN", bn);
   sw = env_int("CCGLIB_B200_SW", sw);
+  const bool want_pair = env_int("CCGLIB_B200_PAIR", kind == kKindMXF4 ? 1 : 0) != 0 &&
+                         d.m > kBlockM;
   if (kind == kKindMXF4) {
-    // two accumulators plus the scale-factor columns must fit 512 tensor-memory columns
-    if (bn == 256) bn = 192;
+    // two accumulators plus 32 scale-factor columns must fit 512 tensor-memory columns: 224
+    // columns for a CTA pair (N of a 256-row MMA is a multiple of 32), else 192
+    if (bn == 256) bn = (want_pair && plan.a_planes == 2) ? 224 : 192;
     if (bn == 64) bn = 128;
     sw = 128;
   }
   if (bn == 64) sw = 128;
-  if ((bn != 64 && bn != 128 && bn != 256 && !(bn == 192 && kind == kKindMXF4)) || (sw != 64 && sw != 128)) {
+  const bool bn_ok = bn == 64 || bn == 128 || bn == 256 ||
+                     (kind == kKindMXF4 && (bn == 192 || (bn == 224 && want_pair &&
+                                                          plan.a_planes == 2)));
+  if (!bn_ok || (sw != 64 && sw != 128)) {
     set_last_error("CCGLIB_B200_BN must be 64, 128 or 256 and CCGLIB_B200_SW 64 or 128");
     return CCGLIB_B200_INVALID_ARGUMENT;
   }
@@ -405,8 +411,7 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
   // 1.25 GHz and it delivers 1116 against 1341 TFLOP/s.
   // The 4-bit path is the exception: it is bound by operand traffic from L2, not by power, and a
   // pair halves the B bytes each SM fetches (5.6 against 5.3 POPS at 4096 x 4096 x 65536).
-  const bool pair = env_int("CCGLIB_B200_PAIR", kind == kKindMXF4 ? 1 : 0) != 0 && sw == 128 &&
-                    bn != 64 && d.m > kBlockM;
+  const bool pair = want_pair && sw == 128 && bn != 64;
   plan.bn = bn;
   plan.sw = sw;
   switch (kind) {
@@ -426,8 +431,9 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
                          : (bn == 192 ? entry<kKindMXF4, 192, 128, 3, IntFromFloat>()
                                       : entry<kKindMXF4, 128, 128, 3, IntFromFloat>());
     } else {
-      plan.kernel = pair ? (bn == 192 ? pair_entry<kKindMXF4, 192, 2, IntFromFloat>()
-                                      : pair_entry<kKindMXF4, 128, 2, IntFromFloat>())
+      plan.kernel = pair ? (bn == 224   ? pair_entry<kKindMXF4, 224, 2, IntFromFloat>()
+                            : bn == 192 ? pair_entry<kKindMXF4, 192, 2, IntFromFloat>()
+                                        : pair_entry<kKindMXF4, 128, 2, IntFromFloat>())
                          : (bn == 192 ? entry<kKindMXF4, 192, 128, 2, IntFromFloat>()
                                       : entry<kKindMXF4, 128, 128, 2, IntFromFloat>());
     }
