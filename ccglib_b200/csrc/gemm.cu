@@ -391,7 +391,25 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
   if (kind == kKindMXF4) {
     // two accumulators plus 32 scale-factor columns must fit 512 tensor-memory columns: 224
     // columns for a CTA pair (N of a 256-row MMA is a multiple of 32), else 192
-    if (bn == 256) bn = (want_pair && plan.a_planes == 2) ? 224 : 192;
+    if (bn == 256) bn = 192;
+    if (want_pair && env_int("CCGLIB_B200_BN", 0) == 0) {
+      // The pair kernel is bound by operand traffic from L2: time per 256 x bn tile goes as
+      // bn / 256 + 1, and there are sms / 2 clusters.  Wider tiles move fewer bytes per flop
+      // (224 columns: 8 % fewer than 192) but may quantise worse on a few waves (4096^2,
+      // batch 1: 1.44 ms with 192 columns, 1.80 ms with 128).
+      const size_t clusters = sms / 2;
+      const size_t rows = d.batch * ceil_div<size_t>(d.m, 2 * kBlockM);
+      double best = 0.0;
+      for (int cand : {224, 192, 128}) {
+        if (cand == 224 && plan.a_planes != 2) continue;
+        const double cost = static_cast<double>(ceil_div(rows * ceil_div<size_t>(d.n, cand), clusters)) *
+                            (cand / 256.0 + 1.0);
+        if (best == 0.0 || cost < best) {
+          best = cost;
+          bn = cand;
+        }
+      }
+    }
     if (bn == 64) bn = 128;
     sw = 128;
   }
