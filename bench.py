@@ -130,9 +130,9 @@ class ClockSampler:
 
 # --------------------------------------------------------------------------- CPU baseline
 
-def cpu_baseline(type_in_name: str, type_out_name: str, K: int, budget_s: float = 12.0) -> dict:
+def cpu_baseline(type_in_name: str, type_out_name: str, K: int, target_s: float = 12.0) -> dict:
     """Times the reference's own CPU GEMM (or the C restatement) on a bounded sample: one batch
-    item of the workload's dtype and K with M = N chosen so the run takes about budget_s."""
+    item of the workload's dtype and K with M = N chosen so the run takes about target_s."""
     import oracle_util as ou
 
     type_in = getattr(ou, type_in_name)
@@ -160,7 +160,7 @@ def cpu_baseline(type_in_name: str, type_out_name: str, K: int, budget_s: float 
     probe_k = min(K, 2048)
     t = run(128, 128, probe_k)
     rate = 8.0 * 128 * 128 * probe_k / max(t, 1e-6)  # ops/s
-    mn = int(math.sqrt(budget_s * rate / (8.0 * K)))
+    mn = int(math.sqrt(target_s * rate / (8.0 * K)))
     mn = max(128, min(4096, (mn // 128) * 128))
     t = run(mn, mn, K)
     ops = 8.0 * mn * mn * K
@@ -445,7 +445,7 @@ def run_reference_arm(args, name):
     vals = []
     base = None
     for i in range(args.warmup + args.steps):
-        base = cpu_baseline(tin, tout, K, budget_s=min(12.0, 90.0 / (args.warmup + args.steps)))
+        base = cpu_baseline(tin, tout, K, target_s=min(12.0, 90.0 / (args.warmup + args.steps)))
         if i >= args.warmup:
             vals.append(base)
     value = float(np.mean([v["value"] for v in vals]))

@@ -507,9 +507,9 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
     const size_t per_item_a = plan.a_planes * d.m * plan.pitch;
     const size_t per_item_b = 2 * d.n * plan.pitch;
     const size_t per_item = per_item_a + per_item_b;
-    const size_t budget = static_cast<size_t>(env_int("CCGLIB_B200_SCRATCH_MB", 8192)) << 20;
+    const size_t cap = static_cast<size_t>(env_int("CCGLIB_B200_SCRATCH_MB", 8192)) << 20;
     // Two lanes pay when every chunk still fills the device several times over: aim at eight
-    // chunks of at least eight waves of tiles each, within half the budget per lane.
+    // chunks of at least eight waves of tiles each, within half the scratch cap per lane.
     const size_t tiles_per_item = ceil_div<size_t>(d.m, plan.kernel.pair ? 2 * kBlockM : kBlockM) *
                                   ceil_div<size_t>(d.n, plan.bn);
     const size_t ctas = plan.kernel.pair ? static_cast<size_t>(plan.sms) / 2 : plan.sms;
@@ -517,7 +517,7 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
     const size_t waves = static_cast<size_t>(env_int("CCGLIB_B200_LANE_WAVES", 8));
     const size_t min_items = ceil_div<size_t>(waves * ctas, tiles_per_item);
     if (lane_chunk < min_items) lane_chunk = min_items;
-    if (lane_chunk * per_item > budget / 2) lane_chunk = budget / 2 / per_item;
+    if (lane_chunk * per_item > cap / 2) lane_chunk = cap / 2 / per_item;
     const bool two_lanes = env_int("CCGLIB_B200_LANES", 2) >= 2 && lane_chunk >= 1 &&
                            ceil_div<size_t>(d.batch, lane_chunk) >= 2;
     size_t chunk;
@@ -525,7 +525,7 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
       chunk = ceil_div(d.batch, ceil_div(d.batch, lane_chunk));  // equal chunks
       plan.lanes = 2;
     } else {
-      chunk = budget / per_item;
+      chunk = cap / per_item;
       if (chunk < 1) chunk = 1;
       if (chunk > d.batch) chunk = d.batch;
       chunk = ceil_div(d.batch, ceil_div(d.batch, chunk));  // equal chunks: no short last launch

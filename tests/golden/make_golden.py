@@ -1,6 +1,7 @@
 """Generate the golden fixtures that pin the CPU oracle.
 
-Run in a container that has the reference checkout (default ``/root/reference``):
+Run where the reference checkout is available (its location is taken from the environment
+variable ``CCGLIB_REFERENCE_ROOT``, see oracle/build.py):
 
     python tests/golden/make_golden.py
 

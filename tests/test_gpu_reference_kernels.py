@@ -3,7 +3,8 @@ unmodified for sm_100a (oracle/build_reference_gpu.py), run on the same seeded i
 library.  1-bit results must be identical; floating-point results must agree within the
 reference's own acceptance rule (test/gemm/fpequals.h:38-53) and each must satisfy the float64
 gate.  The larger cases also time the legacy kernel, which gives the "reference kernel on B200"
-column of the baseline table (written to gpurun_out/reference_gpu_timings.json when possible)."""
+column of the baseline table (written as reference_gpu_timings.json into the directory named by
+CCGLIB_B200_TIMINGS_DIR, when that directory exists)."""
 import json
 import os
 
@@ -119,7 +120,7 @@ def _run_both(name, seed=5, time_it=False):
                          "variant": info["variant"]}
         print("%s: reference kernel %.3f ms (%.1f TOPS), this library %.3f ms (%.1f TOPS)" % (
             name, ms_ref, ops / ms_ref / 1e9, ms_ours, ops / ms_ours / 1e9))
-        out_dir = os.path.join(ROOT, "gpurun_out")
+        out_dir = os.environ.get("CCGLIB_B200_TIMINGS_DIR", os.path.join(ROOT, "gpurun_out"))
         if os.path.isdir(out_dir):
             with open(os.path.join(out_dir, "reference_gpu_timings.json"), "w") as f:
                 json.dump(TIMINGS, f, indent=1)
