@@ -323,6 +323,63 @@ class Workload:
         return {"samples": samples, "ok": worst <= 1.0, "worst_err_over_tol": worst}
 
 
+    def _planes_f64(self, t, b):
+        """(re, im) float64 planes [rows][K] of batch item b of an input tensor, as the GEMM sees
+        them (1-bit: +-1; tf32: low 13 mantissa bits ignored)."""
+        torch = self.torch
+        if self.layout == "interleaved":
+            re, im = t[b, :, :, 0], t[b, :, :, 1]
+        else:
+            re, im = t[b, 0], t[b, 1]
+        re, im = re.to(torch.float32), im.to(torch.float32)
+        if self.layout == "bytes":
+            re, im = 2 * re - 1, 2 * im - 1
+        elif self.dtype == "tf32":
+            re = (re.view(torch.int32) & -8192).view(torch.float32)
+            im = (im.view(torch.int32) & -8192).view(torch.float32)
+        return re.to(torch.float64), im.to(torch.float64)
+
+    def freivalds(self, max_items=4):
+        """Whole-matrix check of up to max_items batch items: C x against A (B^T x) in float64 for
+        a random complex vector x with small integer parts.  Every element of C enters the
+        product, so a wrong tile, edge or plane shows up.  Allowed residual of row m: the
+        per-element gate in its statistical form, 4 sqrt(2K) 2^-24 S(m, n), added in quadrature
+        over n with weights |x_n|, with S(m, n) bounded by the product of the row norms of |A|
+        and |B| (exact equality for 1-bit)."""
+        torch = self.torch
+        g = torch.Generator(device=self.device)
+        g.manual_seed(4321)
+        B, N, K = self.B, self.N, self.K
+        items = sorted({0, B - 1, B // 2, B // 3})[:max_items]
+        worst = 0.0
+        for b in items:
+            xr = torch.randint(-2, 3, (N,), generator=g, device=self.device).to(torch.float64)
+            xi = torch.randint(-2, 3, (N,), generator=g, device=self.device).to(torch.float64)
+            br, bi = self._planes_f64(self.b_in, b)
+            wr = br.T @ xr - bi.T @ xi
+            wi = br.T @ xi + bi.T @ xr
+            b_norm = torch.linalg.vector_norm(br.abs() + bi.abs(), dim=1)
+            spread = torch.sqrt((((xr.abs() + xi.abs()) * b_norm) ** 2).sum())
+            del br, bi
+            ar, ai = self._planes_f64(self.a_in, b)
+            want_re = ar @ wr - ai @ wi
+            want_im = ar @ wi + ai @ wr
+            a_norm = torch.linalg.vector_norm(ar.abs() + ai.abs(), dim=1)
+            del ar, ai
+            cr, ci = self.c[b, 0].to(torch.float64), self.c[b, 1].to(torch.float64)
+            got_re = cr @ xr - ci @ xi
+            got_im = cr @ xi + ci @ xr
+            del cr, ci
+            err = torch.maximum((got_re - want_re).abs(), (got_im - want_im).abs())
+            if self.type_in == self.ou.INT1:
+                if float(err.max()) != 0.0:
+                    return {"items": items, "ok": False, "worst_err_over_tol": float("inf")}
+                continue
+            tol = 4.0 * math.sqrt(2 * K) * 2.0 ** -24 * a_norm * spread + 1e-30
+            worst = max(worst, float((err / tol).max()))
+        return {"items": items, "ok": worst <= 1.0, "worst_err_over_tol": worst}
+
+
 # --------------------------------------------------------------------------- end-to-end pass
 
 class HostPipeline:
@@ -533,6 +590,8 @@ def run_ours(args, name):
     ms_step = float(t[0]) / args.steps
     gemm_ms_max = float(t[1])
     check = wl.spot_check()
+    check["freivalds"] = wl.freivalds()
+    check["ok"] = bool(check["ok"] and check["freivalds"]["ok"])
     wl_bits = wl.bits
     hbm_gb = wl.hbm_bytes() / 1e9
     launches = wl.launches_per_step * args.steps
