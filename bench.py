@@ -52,6 +52,10 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "c2_f16_opt_8192_b64"
 
+# value-type codes of the C ABI (= the reference's ValueType ordinals) and their widths in bits
+TYPE_CODE = {"INT1": 0, "INT32": 1, "BF16": 2, "E4M3": 3, "E5M2": 4, "F16": 5, "F32": 6}
+TYPE_BITS = {0: 1, 1: 32, 2: 16, 3: 8, 4: 8, 5: 16, 6: 32}
+
 # DRAM bytes (read + write) of one GEMM launch per batch item, from the ncu capture summarised in
 # profiles/cgemm_tcgen05_f16_opt_8192_batch2_ncu_full.md (6.79 GB for 2 items; items are walked
 # one after another, so traffic grows in proportion to the batch).
@@ -178,17 +182,16 @@ class Workload:
     def __init__(self, name: str, batch: int, device):
         import torch
 
-        import oracle_util as ou
         from ccglib_b200 import capi
 
-        self.torch, self.capi, self.ou = torch, capi, ou
+        self.torch, self.capi = torch, capi
         dtype, tin, tout, _, M, N, K, variant, layout = WORKLOADS[name]
         self.name, self.dtype, self.B, self.M, self.N, self.K = name, dtype, batch, M, N, K
-        self.type_in, self.type_out = getattr(ou, tin), getattr(ou, tout)
+        self.type_in, self.type_out = TYPE_CODE[tin], TYPE_CODE[tout]
         self.variant = capi.OPT if variant == "opt" else capi.BASIC
         self.layout = layout
         self.device = device
-        self.bits = ou.BITS[self.type_in]
+        self.bits = TYPE_BITS[self.type_in]
         self.flops = 8.0 * M * N * K * batch
         self.launches_per_step = 1
         self.m_blk, self.n_blk, self.k_c = capi.gemm_dims(self.type_in, self.type_out, self.variant)
@@ -248,7 +251,7 @@ class Workload:
                                        device=self.device)
             self.a_gemm, self.b_gemm = self.a_tiled, self.b_tiled
             self.launches_per_step += 2
-        out_dt = torch.int32 if self.type_out == self.ou.INT32 else torch.float32
+        out_dt = torch.int32 if self.type_out == TYPE_CODE["INT32"] else torch.float32
         self.c = torch.empty((self.B, 2, self.M, self.N), dtype=out_dt, device=self.device)
         self.plan = capi.GemmPlan(self.B, self.M, self.N, self.K, self.type_in, self.type_out,
                                   variant=self.variant)
@@ -313,7 +316,7 @@ class Workload:
             s_re = float((ar.abs() * br.abs()).sum() + (ai.abs() * bi.abs()).sum())
             s_im = float((ar.abs() * bi.abs()).sum() + (ai.abs() * br.abs()).sum())
             got_re, got_im = float(self.c[b, 0, m, n]), float(self.c[b, 1, m, n])
-            if self.type_in == self.ou.INT1:
+            if self.type_in == TYPE_CODE["INT1"]:
                 if got_re != re or got_im != im:
                     return {"samples": samples, "ok": False, "worst_err_over_tol": float("inf")}
                 continue
@@ -371,7 +374,7 @@ class Workload:
             got_im = cr @ xi + ci @ xr
             del cr, ci
             err = torch.maximum((got_re - want_re).abs(), (got_im - want_im).abs())
-            if self.type_in == self.ou.INT1:
+            if self.type_in == TYPE_CODE["INT1"]:
                 if float(err.max()) != 0.0:
                     return {"items": items, "ok": False, "worst_err_over_tol": float("inf")}
                 continue
@@ -390,14 +393,13 @@ class HostPipeline:
     def __init__(self, name: str, batch: int, device, slice_items: int):
         import torch
 
-        import oracle_util as ou
         from ccglib_b200 import capi
 
         self.torch, self.capi = torch, capi
         dtype, tin, tout, _, M, N, K, variant, layout = WORKLOADS[name]
         self.B, self.M, self.N, self.K = batch, M, N, K
-        self.type_in, self.type_out = getattr(ou, tin), getattr(ou, tout)
-        self.bits = ou.BITS[self.type_in]
+        self.type_in, self.type_out = TYPE_CODE[tin], TYPE_CODE[tout]
+        self.bits = TYPE_BITS[self.type_in]
         if slice_items <= 0:  # about 1 GiB of input per slice
             per_item = 2 * (M + N) * K * (8 if layout == "bytes" else self.bits) // 8
             slice_items = max(1, (1 << 30) // per_item)
