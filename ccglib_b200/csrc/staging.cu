@@ -36,78 +36,79 @@ struct ExpandParams {
   size_t blk, kc_words, row_tiles, k_tiles;
 };
 
-// A warp expands a block of 128 consecutive
-// words of one row, lane l taking words l, l + 32, l + 64, l + 96, so every load instruction reads
-// 128 contiguous bytes and every store instruction writes 512 (nibbles) or 2 x 512 (bytes)
-// contiguous bytes, and the row/plane arithmetic is paid once per 4096 samples.
-template <bool NIBBLES>
+// A warp expands a block of 128 consecutive words of one row, lane l taking words l, l + 32,
+// l + 64, l + 96, so every load instruction reads 128 contiguous bytes and every store instruction
+// writes 512 (nibbles) or 2 x 512 (bytes) contiguous bytes.  One warp per block (no grid-stride
+// loop): the row/plane arithmetic is two divisions per 4096 samples, in 32 bits whenever the
+// number of blocks allows.
+template <bool NIBBLES, typename Index>
 __global__ void __launch_bounds__(256) expand_bits_warp_kernel(const ExpandParams p) {
-  const size_t blocks_per_row = ceil_div<size_t>(p.words, 128);
-  const size_t total = p.batch * 2 * p.rows * blocks_per_row * 32;
-  const size_t plane_bytes = p.rows * p.out_row_bytes;
+  const Index blocks_per_row = static_cast<Index>(ceil_div<size_t>(p.words, 128));
+  const Index rows = static_cast<Index>(p.rows);
+  const size_t unit = blockIdx.x * static_cast<size_t>(blockDim.x / 32) + (threadIdx.x >> 5);
+  if (unit >= p.batch * 2 * p.rows * static_cast<size_t>(blocks_per_row)) return;
   const uint32_t lane = threadIdx.x & 31;
-  for (size_t gid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; gid < total;
-       gid += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    size_t t = gid >> 5;
-    const size_t blk = t % blocks_per_row;
-    t /= blocks_per_row;
-    const size_t r = t % p.rows;
-    t /= p.rows;
-    const size_t c = t & 1;
-    const size_t b = t >> 1;
-    const bool negated_plane = c == 1 && p.planes_out == 3;
-    int8_t *out_row = p.out + ((b * p.planes_out + c) * p.rows + r) * p.out_row_bytes;
-    const size_t rt = r / p.blk, rr = r - rt * p.blk;
+  const Index row_id = static_cast<Index>(unit) / blocks_per_row;
+  const size_t blk = static_cast<Index>(unit) - row_id * blocks_per_row;
+  const Index plane_id = row_id / rows;
+  const size_t r = row_id - plane_id * rows;
+  const size_t c = plane_id & 1;
+  const size_t b = plane_id >> 1;
+  const size_t plane_bytes = p.rows * p.out_row_bytes;
+  const bool negated_plane = c == 1 && p.planes_out == 3;
+  int8_t *out_row = p.out + ((b * p.planes_out + c) * p.rows + r) * p.out_row_bytes;
+  const size_t rt = r / p.blk, rr = r - rt * p.blk;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const size_t u = blk * 128 + i * 32 + lane;  // word within the row
-      if (u >= p.words) continue;
-      size_t src;
-      if (p.tiled) {
-        const size_t kt = u / p.kc_words, uu = u - kt * p.kc_words;
-        src = ((((b * p.row_tiles + rt) * p.k_tiles + kt) * 2 + c) * p.blk + rr) * p.kc_words + uu;
-      } else {
-        src = ((b * 2 + c) * p.rows + r) * p.words + u;
+  for (int i = 0; i < 4; ++i) {
+    const size_t u = blk * 128 + i * 32 + lane;  // word within the row
+    if (u >= p.words) continue;
+    size_t src;
+    if (p.tiled) {
+      const size_t kt = u / p.kc_words, uu = u - kt * p.kc_words;
+      src = ((((b * p.row_tiles + rt) * p.k_tiles + kt) * 2 + c) * p.blk + rr) * p.kc_words + uu;
+    } else {
+      src = ((b * 2 + c) * p.rows + r) * p.words + u;
+    }
+    const uint32_t w = __ldg(p.in + src);
+    const size_t bit0 = u * 32;
+    const int valid = static_cast<int>(p.k_bits - bit0 < 32 ? p.k_bits - bit0 : 32);
+    if constexpr (NIBBLES) {
+      // 32 samples -> 16 bytes: sample i in nibble i; +1 = 0x2 (e2m1 1.0), -1 = 0xA, padding = 0
+      uint32_t pos[4], neg[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t sign = spread_byte((w >> (8 * q)) & 0xFFu);  // bit j -> bit 4j
+        uint32_t mask = 0xFFFFFFFFu;
+        if (8 * q + 8 > valid) mask = (8 * q >= valid) ? 0u : ((1u << (4 * (valid - 8 * q))) - 1u);
+        pos[q] = (0x22222222u | ((~sign & 0x11111111u) << 3)) & mask;
+        neg[q] = (0x22222222u | (sign << 3)) & mask;
       }
-      const uint32_t w = __ldg(p.in + src);
-      const size_t bit0 = u * 32;
-      const int valid = static_cast<int>(p.k_bits - bit0 < 32 ? p.k_bits - bit0 : 32);
-      if constexpr (NIBBLES) {
-        uint32_t pos[4], neg[4];
+      uint4 *dst = reinterpret_cast<uint4 *>(out_row + u * 16);
+      *dst = make_uint4(pos[0], pos[1], pos[2], pos[3]);
+      if (negated_plane) {
+        *reinterpret_cast<uint4 *>(reinterpret_cast<int8_t *>(dst) + plane_bytes) =
+            make_uint4(neg[0], neg[1], neg[2], neg[3]);
+      }
+    } else {
+      // 32 samples -> 32 signed bytes: +1 = 0x01, -1 = 0xFF, padding = 0
+      uint32_t pos[8], neg[8];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t sign = spread_byte((w >> (8 * q)) & 0xFFu);
-          uint32_t mask = 0xFFFFFFFFu;
-          if (8 * q + 8 > valid) mask = (8 * q >= valid) ? 0u : ((1u << (4 * (valid - 8 * q))) - 1u);
-          pos[q] = (0x22222222u | ((~sign & 0x11111111u) << 3)) & mask;
-          neg[q] = (0x22222222u | (sign << 3)) & mask;
-        }
-        uint4 *dst = reinterpret_cast<uint4 *>(out_row + u * 16);
-        *dst = make_uint4(pos[0], pos[1], pos[2], pos[3]);
-        if (negated_plane) {
-          *reinterpret_cast<uint4 *>(reinterpret_cast<int8_t *>(dst) + plane_bytes) =
-              make_uint4(neg[0], neg[1], neg[2], neg[3]);
-        }
-      } else {
-        uint32_t pos[8], neg[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const uint32_t y = spread_nibble((w >> (4 * q)) & 0xFu);
-          uint32_t mask = 0xFFFFFFFFu;
-          if (4 * q + 4 > valid) mask = (4 * q >= valid) ? 0u : ((1u << (8 * (valid - 4 * q))) - 1u);
-          pos[q] = (0xFFFFFFFFu - y * 0xFEu) & mask;
-          neg[q] = (0x01010101u + y * 0xFEu) & mask;
-        }
-        int8_t *dst = out_row + u * 32;
-        const bool second = u * 32 + 16 < p.out_row_bytes;
-        *reinterpret_cast<uint4 *>(dst) = make_uint4(pos[0], pos[1], pos[2], pos[3]);
-        if (second) *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(pos[4], pos[5], pos[6], pos[7]);
-        if (negated_plane) {
-          int8_t *dn = dst + plane_bytes;
-          *reinterpret_cast<uint4 *>(dn) = make_uint4(neg[0], neg[1], neg[2], neg[3]);
-          if (second) {
-            *reinterpret_cast<uint4 *>(dn + 16) = make_uint4(neg[4], neg[5], neg[6], neg[7]);
-          }
+      for (int q = 0; q < 8; ++q) {
+        const uint32_t y = spread_nibble((w >> (4 * q)) & 0xFu);
+        uint32_t mask = 0xFFFFFFFFu;
+        if (4 * q + 4 > valid) mask = (4 * q >= valid) ? 0u : ((1u << (8 * (valid - 4 * q))) - 1u);
+        pos[q] = (0xFFFFFFFFu - y * 0xFEu) & mask;  // 1 -> 0x01, 0 -> 0xFF
+        neg[q] = (0x01010101u + y * 0xFEu) & mask;  // 1 -> 0xFF, 0 -> 0x01
+      }
+      int8_t *dst = out_row + u * 32;
+      const bool second = u * 32 + 16 < p.out_row_bytes;  // the row pitch is a multiple of 16
+      *reinterpret_cast<uint4 *>(dst) = make_uint4(pos[0], pos[1], pos[2], pos[3]);
+      if (second) *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(pos[4], pos[5], pos[6], pos[7]);
+      if (negated_plane) {
+        int8_t *dn = dst + plane_bytes;
+        *reinterpret_cast<uint4 *>(dn) = make_uint4(neg[0], neg[1], neg[2], neg[3]);
+        if (second) {
+          *reinterpret_cast<uint4 *>(dn + 16) = make_uint4(neg[4], neg[5], neg[6], neg[7]);
         }
       }
     }
@@ -160,16 +161,29 @@ int launch_expand_bits(const void *d_in, void *d_out, size_t batch, size_t rows,
   p.kc_words = k_c_bits / 32;
   p.row_tiles = ceil_div<size_t>(rows, blk);
   p.k_tiles = ceil_div<size_t>(p.words, p.kc_words);
-  {
-    const size_t total_w = batch * 2 * rows * ceil_div<size_t>(p.words, 128) * 32;
-    if (nibbles) {
-      expand_bits_warp_kernel<true><<<grid_for(total_w, 256), 256, 0, stream>>>(p);
-    } else {
-      expand_bits_warp_kernel<false><<<grid_for(total_w, 256), 256, 0, stream>>>(p);
-    }
-    CCGLIB_CUDA_TRY(cudaGetLastError());
-    return CCGLIB_B200_OK;
+  const size_t units = batch * 2 * rows * ceil_div<size_t>(p.words, 128);  // one warp each
+  const size_t blocks = ceil_div<size_t>(units, 8);
+  if (blocks > 0x7FFFFFFFull) {
+    set_last_error("expand_bits: too many rows for one launch");
+    return CCGLIB_B200_INVALID_ARGUMENT;
   }
+  const unsigned grid = static_cast<unsigned>(blocks);
+  const bool narrow = units <= 0xFFFFFFFFull;
+  if (nibbles) {
+    if (narrow) {
+      expand_bits_warp_kernel<true, uint32_t><<<grid, 256, 0, stream>>>(p);
+    } else {
+      expand_bits_warp_kernel<true, size_t><<<grid, 256, 0, stream>>>(p);
+    }
+  } else {
+    if (narrow) {
+      expand_bits_warp_kernel<false, uint32_t><<<grid, 256, 0, stream>>>(p);
+    } else {
+      expand_bits_warp_kernel<false, size_t><<<grid, 256, 0, stream>>>(p);
+    }
+  }
+  CCGLIB_CUDA_TRY(cudaGetLastError());
+  return CCGLIB_B200_OK;
 }
 
 int launch_pad_rows(const void *d_in, void *d_out, size_t rows, size_t row_bytes,
