@@ -7,6 +7,7 @@ runs with the operands resident on the device.
     python -m ccglib_b200.benchmark gemm --b 8 --m 8192 --n 8192 --k 8192 --precision_in float16
     python -m ccglib_b200.benchmark transpose --b 8 --m 8192 --n 8192 --precision float16
     python -m ccglib_b200.benchmark packing --n 1073741824 --direction pack
+    python -m ccglib_b200.benchmark gemm --gpus 8 --b 64 --m 8192 --n 8192 --k 8192 --precision_in float16
 
 Several sizes may be given (`--m 1024,2048 --n ... --k ...`).  `--pad` rounds M, N, K up to the
 tile sizes of `GetDimensions`, as the reference's flag does.  `--measure_power` adds the average
@@ -87,9 +88,11 @@ def _ceil(a: int, b: int) -> int:
     return -(-a // b)
 
 
-def bench_gemm(args) -> None:
+def _gemm_on_device(args, device: int, batch: int, barrier, out: list) -> None:
+    """The GEMM timing loop of one GPU on `batch` items; appends (M, N, K, ms, watts) rows."""
     import torch
 
+    torch.cuda.set_device(device)
     tin = PRECISIONS[args.precision_in]
     tout = PRECISIONS[args.precision_out]
     if tin == capi.INT1:
@@ -98,38 +101,81 @@ def bench_gemm(args) -> None:
     axis = capi.INTERLEAVED if args.complex_axis == "interleaved" else capi.PLANAR
     m_blk, n_blk, k_c = capi.gemm_dims(tin, tout, variant)
     stream = int(torch.cuda.current_stream().cuda_stream)
-    meter = _EnergyMeter(args.device) if args.measure_power else None
-    if args.csv:
-        print("#M,N,K,runtime_ms,tops" + (",watt,tops_per_joule" if meter else ""))
+    meter = _EnergyMeter(device) if args.measure_power else None
+    dev = "cuda:%d" % device
     first = True
     for _ in range(args.nr_benchmarks):
         for M, N, K in zip(_sizes(args.m), _sizes(args.n), _sizes(args.k)):
             if args.pad:
                 M, N, K = _ceil(M, m_blk) * m_blk, _ceil(N, n_blk) * n_blk, _ceil(K, k_c) * k_c
             if variant == capi.OPT:  # zero-padded tiled operands
-                a_bytes = args.b * 2 * _ceil(M, m_blk) * m_blk * _ceil(K, k_c) * k_c * BITS[tin] // 8
-                b_bytes = args.b * 2 * _ceil(N, n_blk) * n_blk * _ceil(K, k_c) * k_c * BITS[tin] // 8
+                a_bytes = batch * 2 * _ceil(M, m_blk) * m_blk * _ceil(K, k_c) * k_c * BITS[tin] // 8
+                b_bytes = batch * 2 * _ceil(N, n_blk) * n_blk * _ceil(K, k_c) * k_c * BITS[tin] // 8
             else:
                 row = _ceil(K, 32) * 4 if tin == capi.INT1 else K * BITS[tin] // 8
-                a_bytes, b_bytes = args.b * 2 * M * row, args.b * 2 * N * row
+                a_bytes, b_bytes = batch * 2 * M * row, batch * 2 * N * row
             # operand bytes: 0x3c patterns decode to small finite values in every float type
-            d_a = torch.full((a_bytes,), 0x3C, dtype=torch.uint8, device="cuda")
-            d_b = torch.full((b_bytes,), 0x3C, dtype=torch.uint8, device="cuda")
-            d_c = torch.empty(args.b * 2 * M * N * BITS[tout] // 8, dtype=torch.uint8, device="cuda")
-            plan = capi.GemmPlan(args.b, M, N, K, tin, tout, variant=variant, c_complex_axis=axis)
+            d_a = torch.full((a_bytes,), 0x3C, dtype=torch.uint8, device=dev)
+            d_b = torch.full((b_bytes,), 0x3C, dtype=torch.uint8, device=dev)
+            d_c = torch.empty(batch * 2 * M * N * BITS[tout] // 8, dtype=torch.uint8, device=dev)
+            plan = capi.GemmPlan(batch, M, N, K, tin, tout, variant=variant, c_complex_axis=axis)
+            if barrier is not None:
+                barrier.wait()  # all GPUs start the same problem together
             ms, _, watts = _time(
                 lambda: plan.run(d_a.data_ptr(), d_b.data_ptr(), d_c.data_ptr(), stream),
                 args.benchmark_duration, first, meter)
             first = False
-            tops = 8e-9 * args.b * M * N * K / ms
-            if args.csv:
-                print("%d,%d,%d,%g,%g" % (M, N, K, ms, tops) +
-                      (",%g,%g" % (watts, tops / watts) if meter else ""))
-            else:
-                print("%20s %7.4g ms, %7.4g TOps/s" % ("%dx%dx%d" % (M, N, K), ms, tops) +
-                      (", %7.4g W, %7.4g TOps/J" % (watts, tops / watts) if meter else ""))
+            out.append((M, N, K, ms, watts))
             plan.close()
             del d_a, d_b, d_c
+
+
+def bench_gemm(args) -> None:
+    """One GPU (`--device`), or `--gpus N`: the batch is split over GPUs 0..N-1 in contiguous
+    shares (the partition `bench.py` uses), one host thread per GPU, no data-path collective;
+    the reported time is the slowest GPU's and the rate is the whole batch over that time."""
+    import threading
+
+    from .sharding import batch_shares
+
+    power = args.measure_power
+    capi.lib()  # load the library before any thread needs it
+    if args.csv:
+        print("#M,N,K,runtime_ms,tops" + (",watt,tops_per_joule" if power else ""))
+    if args.gpus <= 1:
+        rows: list = []
+        _gemm_on_device(args, args.device, args.b, None, rows)
+        per_gpu = [rows]
+    else:
+        shares = [n for n in batch_shares(args.b, args.gpus) if n > 0]
+        barrier = threading.Barrier(len(shares))
+        per_gpu = [[] for _ in shares]
+        errors: list = []
+
+        def work(g):
+            try:
+                _gemm_on_device(args, g, shares[g], barrier, per_gpu[g])
+            except BaseException as exc:  # surface the failure instead of a hung barrier
+                errors.append(exc)
+                barrier.abort()
+
+        threads = [threading.Thread(target=work, args=(g,)) for g in range(len(shares))]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        if errors:
+            raise errors[0]
+    for i, (M, N, K, _, _) in enumerate(per_gpu[0]):
+        ms = max(rows[i][3] for rows in per_gpu)
+        tops = 8e-9 * args.b * M * N * K / ms
+        watts = sum(rows[i][4] for rows in per_gpu) if power else None
+        if args.csv:
+            print("%d,%d,%d,%g,%g" % (M, N, K, ms, tops) +
+                  (",%g,%g" % (watts, tops / watts) if power else ""))
+        else:
+            print("%20s %7.4g ms, %7.4g TOps/s" % ("%dx%dx%d" % (M, N, K), ms, tops) +
+                  (", %7.4g W, %7.4g TOps/J" % (watts, tops / watts) if power else ""))
 
 
 def bench_transpose(args) -> None:
@@ -210,6 +256,8 @@ def main(argv=None) -> int:
     g.add_argument("--n", required=True)
     g.add_argument("--k", required=True)
     g.add_argument("--pad", action="store_true")
+    g.add_argument("--gpus", type=int, default=1,
+                   help="split the batch over this many GPUs (0..N-1), one host thread each")
     g.add_argument("--precision_in", default="float32", choices=sorted(PRECISIONS))
     g.add_argument("--precision_out", default="float32", choices=sorted(PRECISIONS))
     g.add_argument("--variant", default="opt", choices=["basic", "opt"])

@@ -48,3 +48,14 @@ def test_gemm_cli_pad_and_power():
     assert rows[0][:3] == ["1024", "1024", "1024"]
     watts, tops_per_joule = float(rows[0][5]), float(rows[0][6])
     assert 10 < watts < 1500 and tops_per_joule > 0
+
+
+def test_gemm_cli_multi_gpu():
+    """--gpus N splits the batch over N GPUs (one host thread each) and reports the aggregate."""
+    import torch
+
+    n = min(2, torch.cuda.device_count())
+    header, rows = _run("gemm", "--gpus", str(n), "--b", "5", "--m", "512", "--n", "512", "--k",
+                        "1024", "--precision_in", "float16")
+    assert header == "#M,N,K,runtime_ms,tops"
+    assert rows[0][:3] == ["512", "512", "1024"] and float(rows[0][4]) > 0
