@@ -59,3 +59,17 @@ def test_gemm_cli_multi_gpu():
                         "1024", "--precision_in", "float16")
     assert header == "#M,N,K,runtime_ms,tops"
     assert rows[0][:3] == ["512", "512", "1024"] and float(rows[0][4]) > 0
+
+
+def test_tune_cli():
+    res = subprocess.run([sys.executable, "-m", "ccglib_b200.tune", "--b", "2", "--m", "512", "--n",
+                          "512", "--k", "1024", "--precision_in", "float16", "--duration", "0.02"],
+                         cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr
+    assert "plan's choice" in res.stdout and "best fixed form" in res.stdout
+    res = subprocess.run([sys.executable, "-m", "ccglib_b200.tune", "--m", "512", "--n", "512",
+                          "--k", "2048", "--precision_in", "int1", "--data", "random",
+                          "--duration", "0.02"], cwd=ROOT, capture_output=True, text=True,
+                         timeout=300)
+    assert res.returncode == 0, res.stderr
+    assert "pair, 224 columns" in res.stdout
