@@ -1,0 +1,84 @@
+"""Seeded random shapes through every layout the GEMM accepts: ragged M, N, K around the tile
+edges of all kernel forms (64 / 128 / 256-column tiles, 256-row CTA pairs with 128 / 192 / 224
+columns on the 1-bit path), batch sizes that do and do not fill the device, planar / interleaved
+and row- / col-major C, alpha and beta.  1-bit results must be identical to the oracle; floating
+point must agree with it under the reference's own acceptance rule (test/gemm/fpequals.h:38-53)."""
+import numpy as np
+import pytest
+
+import gpu_util as gu
+import oracle_util as ou
+from ccglib_b200 import capi
+from test_gpu_gemm import make_inputs
+
+pytestmark = pytest.mark.gpu
+
+EDGES = [1, 7, 63, 64, 65, 127, 128, 129, 191, 192, 193, 223, 224, 225, 255, 256, 257, 300, 448,
+         449, 511, 513, 640]
+
+
+def _cases(seed, count, types):
+    rng = np.random.default_rng(seed)
+    out = []
+    for i in range(count):
+        type_in, type_out = types[int(rng.integers(len(types)))]
+        M = int(rng.choice(EDGES))
+        N = int(rng.choice(EDGES))
+        if type_in == ou.INT1:
+            K = int(rng.choice([32, 70, 256, 1000, 1056, 4128]))
+        else:
+            K = int(rng.choice([8, 40, 64, 100, 264, 520]))
+        B = int(rng.choice([1, 2, 5]))
+        variant = capi.OPT if rng.integers(2) else capi.BASIC
+        if type_in == ou.INT1 and variant == capi.OPT:
+            K = -(-K // 32) * 32  # the tiling pass moves whole 32-sample words
+        c_axis = capi.INTERLEAVED if (variant == capi.OPT and rng.integers(2)) else capi.PLANAR
+        c_order = capi.COL_MAJOR if rng.integers(2) else capi.ROW_MAJOR
+        scaled = bool(rng.integers(3) == 0)
+        out.append((i, type_in, type_out, B, M, N, K, variant, c_axis, c_order, scaled))
+    return out
+
+
+def _run(case):
+    i, type_in, type_out, B, M, N, K, variant, c_axis, c_order, scaled = case
+    a, b = make_inputs(1000 + i, type_in, B, M, N, K)
+    alpha, beta, c0_canon, c0 = (1.0, 0.0), (0.0, 0.0), None, None
+    if scaled:
+        rng = np.random.default_rng(2000 + i)
+        if type_in == ou.INT1:
+            alpha, beta = (2.0, -1.0), (1.0, 3.0)
+            c0_canon = rng.integers(-40, 40, size=(B, 2, M, N), dtype=np.int32)
+        else:
+            alpha, beta = (0.5, -1.25), (0.75, 0.5)
+            c0_canon = ou.random_storage(rng, (B, 2, M, N), type_out, "uniform")
+        # the caller's C in the requested layout
+        if c_axis == capi.PLANAR:
+            c0 = c0_canon if c_order == capi.ROW_MAJOR else c0_canon.transpose(0, 1, 3, 2)
+        else:
+            c0 = (c0_canon.transpose(0, 2, 3, 1) if c_order == capi.ROW_MAJOR
+                  else c0_canon.transpose(0, 3, 2, 1))
+        c0 = np.ascontiguousarray(c0)
+    got = gu.run_gemm(type_in, type_out, a, b, B, M, N, K, variant=variant, c_axis=c_axis,
+                      c_order=c_order, alpha=alpha, beta=beta, c0=c0)
+    got = gu.canonical_c(got, B, M, N, c_axis, c_order)
+    want = gu.oracle_batch(type_in, type_out, a, b, B, M, N, K, alpha, beta, c0_canon)
+    return got, want, a, b
+
+
+@pytest.mark.parametrize("case", _cases(17, 40, [(ou.INT1, ou.INT32)]),
+                         ids=lambda c: "i1-%d-B%d-%dx%dx%d" % (c[0], c[3], c[4], c[5], c[6]))
+def test_int1_random_shapes_bit_exact(case):
+    got, want, _, _ = _run(case)
+    assert np.array_equal(got, want)
+
+
+FLOATS = [(ou.F16, ou.F32), (ou.BF16, ou.F32), (ou.F32, ou.F32), (ou.E4M3, ou.F32),
+          (ou.E5M2, ou.F32), (ou.F16, ou.F16), (ou.BF16, ou.BF16), (ou.F32, ou.F16)]
+
+
+@pytest.mark.parametrize("case", _cases(23, 40, FLOATS),
+                         ids=lambda c: "%s-%d-B%d-%dx%dx%d" % (ou.TYPE_NAMES[c[1]], c[0], c[3],
+                                                                c[4], c[5], c[6]))
+def test_float_random_shapes_reference_rule(case):
+    got, want, _, _ = _run(case)
+    gu.assert_close_reference_rule(got, want, case[1], case[2])
