@@ -360,6 +360,18 @@ def test_staged_two_lanes(monkeypatch, type_in, type_out, K):
         gu.assert_close_fp64(got, type_in, type_out, a, b, K)
 
 
+def test_staged_two_lanes_by_default_on_a_large_batch():
+    """A 1-bit batch of many tile waves is split into chunks over two lanes without any override."""
+    B, M, N, K = 64, 1024, 1024, 256
+    plan = capi.GemmPlan(B, M, N, K, ou.INT1, ou.INT32, variant=capi.BASIC)
+    launches = plan.launches
+    plan.close()
+    assert launches >= 6 and launches % 3 == 0  # at least two chunks of (expand A, expand B, GEMM)
+    a, b = make_inputs(33, ou.INT1, B, M, N, K)
+    got = gu.run_gemm(ou.INT1, ou.INT32, a, b, B, M, N, K, variant=capi.BASIC).reshape(B, 2, M, N)
+    assert np.array_equal(got, gu.oracle_batch(ou.INT1, ou.INT32, a, b, B, M, N, K))
+
+
 def test_run_twice_same_plan_is_deterministic():
     import torch
 
