@@ -100,7 +100,11 @@ CCGLIB_B200_API int ccglib_b200_gemm_dims(int type_in, int type_out, int variant
 CCGLIB_B200_API int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc, ccglib_b200_gemm_plan **plan);
 
 /* Enqueue the GEMM.  Replaces ccglib::mma::GEMM::Run(CUdeviceptr a, b, c)
- * (reference src/mma/GEMM.cpp:99-108,263-268). */
+ * (reference src/mma/GEMM.cpp:99-108,263-268).  Never allocates and never synchronises the
+ * host.  All work is ordered after what `stream` holds at the call and before anything
+ * enqueued on it afterwards; a staged plan with several batch chunks forks two internal streams
+ * off `stream` for the chunks and joins them back before returning.  One plan must not run on
+ * two streams at the same time (its scratch and tensor-map cache are per plan). */
 CCGLIB_B200_API int ccglib_b200_gemm_run(ccglib_b200_gemm_plan *plan, const void *d_a, const void *d_b, void *d_c,
                          void *stream);
 
