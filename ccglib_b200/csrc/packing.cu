@@ -33,13 +33,21 @@ __device__ __forceinline__ uint32_t spread4(uint32_t nibble) {
 // pair are always active together.
 __global__ void __launch_bounds__(256)
 pack_planar_kernel(const uint4 *__restrict__ in, uint32_t *__restrict__ out, size_t units) {
-  for (size_t base = blockIdx.x * static_cast<size_t>(blockDim.x); base < units;
-       base += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const size_t u = base + threadIdx.x;
-    uint32_t bits = 0;
-    if (u < units) bits = squeeze16(__ldg(in + u));
-    const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, bits, 1);
-    if (u < units && (threadIdx.x & 1) == 0) out[u >> 1] = bits | (other << 16);
+  constexpr int kUnroll = 4;  // independent 16-byte loads in flight per thread
+  const size_t span = static_cast<size_t>(blockDim.x) * kUnroll;
+  for (size_t base = blockIdx.x * span; base < units; base += static_cast<size_t>(gridDim.x) * span) {
+    uint32_t bits[kUnroll];
+#pragma unroll
+    for (int j = 0; j < kUnroll; ++j) {
+      const size_t u = base + j * blockDim.x + threadIdx.x;
+      bits[j] = u < units ? squeeze16(__ldg(in + u)) : 0u;
+    }
+#pragma unroll
+    for (int j = 0; j < kUnroll; ++j) {
+      const size_t u = base + j * blockDim.x + threadIdx.x;
+      const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, bits[j], 1);
+      if (u < units && (threadIdx.x & 1) == 0) out[u >> 1] = bits[j] | (other << 16);
+    }
   }
 }
 
@@ -48,28 +56,36 @@ pack_planar_kernel(const uint4 *__restrict__ in, uint32_t *__restrict__ out, siz
 __global__ void __launch_bounds__(256)
 pack_interleaved_kernel(const uint4 *__restrict__ in, uint32_t *__restrict__ out, size_t units,
                         size_t imag_word_offset) {
-  for (size_t base = blockIdx.x * static_cast<size_t>(blockDim.x); base < units;
-       base += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const size_t u = base + threadIdx.x;
-    uint32_t re = 0, im = 0;
-    if (u < units) {
-      const uint4 v = __ldg(in + u);
-      // bytes r0 i0 r1 i1 | ... : gather real bytes and imaginary bytes, then squeeze
-      const uint32_t r01 = __byte_perm(v.x, v.y, 0x6420u), i01 = __byte_perm(v.x, v.y, 0x7531u);
-      const uint32_t r23 = __byte_perm(v.z, v.w, 0x6420u), i23 = __byte_perm(v.z, v.w, 0x7531u);
-      re = squeeze4(r01) | (squeeze4(r23) << 4);
-      im = squeeze4(i01) | (squeeze4(i23) << 4);
+  constexpr int kUnroll = 4;
+  const size_t span = static_cast<size_t>(blockDim.x) * kUnroll;
+  for (size_t base = blockIdx.x * span; base < units; base += static_cast<size_t>(gridDim.x) * span) {
+    uint4 v[kUnroll];
+#pragma unroll
+    for (int j = 0; j < kUnroll; ++j) {
+      const size_t u = base + j * blockDim.x + threadIdx.x;
+      v[j] = u < units ? __ldg(in + u) : make_uint4(0, 0, 0, 0);
     }
-    const uint32_t shift = (threadIdx.x & 3) * 8;
-    re <<= shift;
-    im <<= shift;
-    re |= __shfl_xor_sync(0xFFFFFFFFu, re, 1);
-    im |= __shfl_xor_sync(0xFFFFFFFFu, im, 1);
-    re |= __shfl_xor_sync(0xFFFFFFFFu, re, 2);
-    im |= __shfl_xor_sync(0xFFFFFFFFu, im, 2);
-    if (u < units && (threadIdx.x & 3) == 0) {
-      out[u >> 2] = re;
-      out[(u >> 2) + imag_word_offset] = im;
+#pragma unroll
+    for (int j = 0; j < kUnroll; ++j) {
+      const size_t u = base + j * blockDim.x + threadIdx.x;
+      // bytes r0 i0 r1 i1 | ... : gather real bytes and imaginary bytes, then squeeze
+      const uint32_t r01 = __byte_perm(v[j].x, v[j].y, 0x6420u);
+      const uint32_t i01 = __byte_perm(v[j].x, v[j].y, 0x7531u);
+      const uint32_t r23 = __byte_perm(v[j].z, v[j].w, 0x6420u);
+      const uint32_t i23 = __byte_perm(v[j].z, v[j].w, 0x7531u);
+      uint32_t re = squeeze4(r01) | (squeeze4(r23) << 4);
+      uint32_t im = squeeze4(i01) | (squeeze4(i23) << 4);
+      const uint32_t shift = (threadIdx.x & 3) * 8;
+      re <<= shift;
+      im <<= shift;
+      re |= __shfl_xor_sync(0xFFFFFFFFu, re, 1);
+      im |= __shfl_xor_sync(0xFFFFFFFFu, im, 1);
+      re |= __shfl_xor_sync(0xFFFFFFFFu, re, 2);
+      im |= __shfl_xor_sync(0xFFFFFFFFu, im, 2);
+      if (u < units && (threadIdx.x & 3) == 0) {
+        out[u >> 2] = re;
+        out[(u >> 2) + imag_word_offset] = im;
+      }
     }
   }
 }
@@ -99,16 +115,27 @@ pack_scalar_kernel(const uint8_t *__restrict__ in, uint32_t *__restrict__ out, s
 // Backward: unit = 16 output bytes.
 __global__ void __launch_bounds__(256)
 unpack_kernel(const uint32_t *__restrict__ in, uint8_t *__restrict__ out, size_t n) {
+  constexpr int kUnroll = 4;  // independent loads, then independent 16-byte stores, per thread
   const size_t units = n / 16;
-  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-  const size_t tid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
-  for (size_t u = tid; u < units; u += stride) {
-    const uint32_t half = (__ldg(in + (u >> 1)) >> ((u & 1) * 16)) & 0xFFFFu;
-    *reinterpret_cast<uint4 *>(out + u * 16) =
-        make_uint4(spread4(half & 0xFu), spread4((half >> 4) & 0xFu), spread4((half >> 8) & 0xFu),
-                   spread4((half >> 12) & 0xFu));
+  const size_t span = static_cast<size_t>(blockDim.x) * kUnroll;
+  for (size_t base = blockIdx.x * span; base < units; base += static_cast<size_t>(gridDim.x) * span) {
+    uint32_t half[kUnroll];
+#pragma unroll
+    for (int j = 0; j < kUnroll; ++j) {
+      const size_t u = base + j * blockDim.x + threadIdx.x;
+      half[j] = u < units ? (__ldg(in + (u >> 1)) >> ((u & 1) * 16)) & 0xFFFFu : 0u;
+    }
+#pragma unroll
+    for (int j = 0; j < kUnroll; ++j) {
+      const size_t u = base + j * blockDim.x + threadIdx.x;
+      if (u < units) {
+        *reinterpret_cast<uint4 *>(out + u * 16) =
+            make_uint4(spread4(half[j] & 0xFu), spread4((half[j] >> 4) & 0xFu),
+                       spread4((half[j] >> 8) & 0xFu), spread4((half[j] >> 12) & 0xFu));
+      }
+    }
   }
-  if (tid == 0) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
     for (size_t t = units * 16; t < n; ++t) out[t] = (in[t / 32] >> (t % 32)) & 1u;
   }
 }
@@ -145,7 +172,7 @@ extern "C" int ccglib_b200_pack_run(size_t n, int direction, int input_complex_a
       set_last_error("pack_run: output must be 16-byte aligned");
       return CCGLIB_B200_INVALID_ARGUMENT;
     }
-    unpack_kernel<<<grid_for(n / 16 + 1), 256, 0, stream>>>(static_cast<const uint32_t *>(d_in),
+    unpack_kernel<<<grid_for(ceil_div<size_t>(n / 16, 4) + 1), 256, 0, stream>>>(static_cast<const uint32_t *>(d_in),
                                                            static_cast<uint8_t *>(d_out), n);
   } else if (direction == CCGLIB_B200_FORWARD) {
     const bool vec = aligned16(d_in) && (interleaved ? n % 64 == 0 : n % 32 == 0);
@@ -154,10 +181,10 @@ extern "C" int ccglib_b200_pack_run(size_t n, int direction, int input_complex_a
           static_cast<const uint8_t *>(d_in), static_cast<uint32_t *>(d_out), n,
           interleaved ? 1 : 0);
     } else if (interleaved) {
-      pack_interleaved_kernel<<<grid_for(n / 16), 256, 0, stream>>>(
+      pack_interleaved_kernel<<<grid_for(ceil_div<size_t>(n / 16, 4)), 256, 0, stream>>>(
           static_cast<const uint4 *>(d_in), static_cast<uint32_t *>(d_out), n / 16, n / 64);
     } else {
-      pack_planar_kernel<<<grid_for(n / 16), 256, 0, stream>>>(
+      pack_planar_kernel<<<grid_for(ceil_div<size_t>(n / 16, 4)), 256, 0, stream>>>(
           static_cast<const uint4 *>(d_in), static_cast<uint32_t *>(d_out), n / 16);
     }
   } else {
