@@ -75,13 +75,22 @@ __global__ void __launch_bounds__(256) expand_bits_warp_kernel(const ExpandParam
     if constexpr (NIBBLES) {
       // 32 samples -> 16 bytes: sample i in nibble i; +1 = 0x2 (e2m1 1.0), -1 = 0xA, padding = 0
       uint32_t pos[4], neg[4];
+      if (valid == 32) {  // every word but possibly the last of a row: no padding mask
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint32_t sign = spread_byte((w >> (8 * q)) & 0xFFu);  // bit j -> bit 4j
-        uint32_t mask = 0xFFFFFFFFu;
-        if (8 * q + 8 > valid) mask = (8 * q >= valid) ? 0u : ((1u << (4 * (valid - 8 * q))) - 1u);
-        pos[q] = (0x22222222u | ((~sign & 0x11111111u) << 3)) & mask;
-        neg[q] = (0x22222222u | (sign << 3)) & mask;
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t sign = spread_byte(__byte_perm(w, 0, 0x4440 + q));  // bit j -> bit 4j
+          neg[q] = 0x22222222u | (sign << 3);
+          pos[q] = neg[q] ^ 0x88888888u;
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t sign = spread_byte((w >> (8 * q)) & 0xFFu);
+          uint32_t mask = 0xFFFFFFFFu;
+          if (8 * q + 8 > valid) mask = (8 * q >= valid) ? 0u : ((1u << (4 * (valid - 8 * q))) - 1u);
+          pos[q] = (0x22222222u | ((~sign & 0x11111111u) << 3)) & mask;
+          neg[q] = (0x22222222u | (sign << 3)) & mask;
+        }
       }
       uint4 *dst = reinterpret_cast<uint4 *>(out_row + u * 16);
       *dst = make_uint4(pos[0], pos[1], pos[2], pos[3]);
