@@ -595,7 +595,10 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
   const bool pair = plan.kernel.pair;
   p.tiles_m = static_cast<uint32_t>(ceil_div<size_t>(d.m, pair ? 2 * kBlockM : kBlockM));
   p.tiles_n = static_cast<uint32_t>(ceil_div<size_t>(d.n, plan.bn));
-  p.group_n = static_cast<uint32_t>(env_int("CCGLIB_B200_GROUP", plan.bn == 256 ? 4 : 8));
+  // column-panel width of the tile walk: 4 for 256-column tiles; 8 for narrower ones, except
+  // on short matrices (one or two row tiles: +2 % on 256 x 2048 x 512)
+  p.group_n = static_cast<uint32_t>(
+      env_int("CCGLIB_B200_GROUP", (plan.bn == 256 || p.tiles_m <= 2) ? 4 : 8));
   if (p.group_n == 0) p.group_n = 1;
   const size_t tiles = nb * p.tiles_m * p.tiles_n;
   if (tiles > 0x7FFFFFFFull) {
