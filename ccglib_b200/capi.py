@@ -23,7 +23,11 @@ EXPORTS = [
     "ccglib_b200_gemm_plan_launches",
     "ccglib_b200_transpose_run", "ccglib_b200_pack_run", "ccglib_b200_device_status",
     "ccglib_b200_status_string", "ccglib_b200_last_error",
-    "ccglib_b200_gemm_int1_static_scratch",
+    "ccglib_b200_gemm_int1_static_scratch", "ccglib_b200_selftest_wait_timeout",
+    "ccglib_b200_pipeline_create", "ccglib_b200_pipeline_run", "ccglib_b200_pipeline_run_host",
+    "ccglib_b200_pipeline_host_slice", "ccglib_b200_pipeline_set_host_slice",
+    "ccglib_b200_pipeline_launches", "ccglib_b200_pipeline_scratch_bytes",
+    "ccglib_b200_pipeline_destroy",
 ]
 
 
@@ -35,6 +39,16 @@ class GemmDesc(ctypes.Structure):
                 ("c_mem_order", ctypes.c_int), ("alpha_re", ctypes.c_float),
                 ("alpha_im", ctypes.c_float), ("beta_re", ctypes.c_float),
                 ("beta_im", ctypes.c_float)]
+
+
+class PipelineDesc(ctypes.Structure):
+    _fields_ = [("batch", ctypes.c_size_t), ("m", ctypes.c_size_t), ("n", ctypes.c_size_t),
+                ("k", ctypes.c_size_t), ("type_in", ctypes.c_int), ("type_out", ctypes.c_int),
+                ("variant", ctypes.c_int), ("input_complex_axis", ctypes.c_int),
+                ("output_complex_axis", ctypes.c_int), ("a_mem_order", ctypes.c_int),
+                ("b_mem_order", ctypes.c_int), ("c_mem_order", ctypes.c_int),
+                ("alpha_re", ctypes.c_float), ("alpha_im", ctypes.c_float),
+                ("beta_re", ctypes.c_float), ("beta_im", ctypes.c_float)]
 
 
 class Error(RuntimeError):
@@ -80,6 +94,25 @@ def lib() -> ctypes.CDLL:
         L.ccglib_b200_pack_run.restype = ci
         L.ccglib_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
         L.ccglib_b200_device_status.restype = ci
+        L.ccglib_b200_selftest_wait_timeout.argtypes = [ctypes.c_longlong, ci,
+                                                        ctypes.POINTER(ctypes.c_longlong * 2)]
+        L.ccglib_b200_selftest_wait_timeout.restype = ci
+        L.ccglib_b200_pipeline_create.argtypes = [ctypes.POINTER(PipelineDesc), ctypes.POINTER(vp)]
+        L.ccglib_b200_pipeline_create.restype = ci
+        L.ccglib_b200_pipeline_run.argtypes = [vp, vp, vp, vp, vp]
+        L.ccglib_b200_pipeline_run.restype = ci
+        L.ccglib_b200_pipeline_run_host.argtypes = [vp, vp, vp, vp, vp]
+        L.ccglib_b200_pipeline_run_host.restype = ci
+        L.ccglib_b200_pipeline_host_slice.argtypes = [vp]
+        L.ccglib_b200_pipeline_host_slice.restype = sz
+        L.ccglib_b200_pipeline_set_host_slice.argtypes = [vp, sz]
+        L.ccglib_b200_pipeline_set_host_slice.restype = ci
+        L.ccglib_b200_pipeline_launches.argtypes = [vp]
+        L.ccglib_b200_pipeline_launches.restype = sz
+        L.ccglib_b200_pipeline_scratch_bytes.argtypes = [vp]
+        L.ccglib_b200_pipeline_scratch_bytes.restype = sz
+        L.ccglib_b200_pipeline_destroy.argtypes = [vp]
+        L.ccglib_b200_pipeline_destroy.restype = ci
         L.ccglib_b200_status_string.argtypes = [ci]
         L.ccglib_b200_status_string.restype = ctypes.c_char_p
         L.ccglib_b200_last_error.argtypes = []
@@ -136,6 +169,53 @@ class GemmPlan:
             pass
 
 
+class Pipeline:
+    """Owns a ccglib_b200_pipeline (the counterpart of a ccglib::pipeline::Pipeline object)."""
+
+    def __init__(self, batch, m, n, k, type_in, type_out, variant=OPT, input_complex_axis=PLANAR,
+                 output_complex_axis=PLANAR, c_mem_order=ROW_MAJOR, a_mem_order=ROW_MAJOR,
+                 b_mem_order=COL_MAJOR, alpha=(1.0, 0.0), beta=(0.0, 0.0)):
+        self.desc = PipelineDesc(batch, m, n, k, type_in, type_out, variant, input_complex_axis,
+                                 output_complex_axis, a_mem_order, b_mem_order, c_mem_order,
+                                 alpha[0], alpha[1], beta[0], beta[1])
+        self._p = ctypes.c_void_p()
+        _check(lib().ccglib_b200_pipeline_create(ctypes.byref(self.desc), ctypes.byref(self._p)))
+
+    @property
+    def launches(self) -> int:
+        return int(lib().ccglib_b200_pipeline_launches(self._p))
+
+    @property
+    def scratch_bytes(self) -> int:
+        return int(lib().ccglib_b200_pipeline_scratch_bytes(self._p))
+
+    @property
+    def host_slice(self) -> int:
+        return int(lib().ccglib_b200_pipeline_host_slice(self._p))
+
+    @host_slice.setter
+    def host_slice(self, items: int) -> None:
+        _check(lib().ccglib_b200_pipeline_set_host_slice(self._p, items))
+
+    def run(self, d_a: int, d_b: int, d_c: int, stream: int = 0) -> None:
+        _check(lib().ccglib_b200_pipeline_run(self._p, d_a, d_b, d_c, stream))
+
+    def run_host(self, h_a: int, h_b: int, h_c: int, stream: int = 0) -> None:
+        """Host pointers of the whole A, B, C; returns when C is complete."""
+        _check(lib().ccglib_b200_pipeline_run_host(self._p, h_a, h_b, h_c, stream))
+
+    def close(self) -> None:
+        if self._p:
+            lib().ccglib_b200_pipeline_destroy(self._p)
+            self._p = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def gemm_int1_static_scratch(batch, m, n, k, d_a, d_b, d_c, stream: int = 0, variant=BASIC,
                              c_complex_axis=PLANAR, c_mem_order=ROW_MAJOR, alpha=(1.0, 0.0),
                              beta=(0.0, 0.0)) -> None:
@@ -154,6 +234,15 @@ def transpose(batch, m, n, m_chunk, n_chunk, nr_bits, input_complex_axis, d_in, 
 
 def pack(n, direction, input_complex_axis, d_in, d_out, stream: int = 0) -> None:
     _check(lib().ccglib_b200_pack_run(n, direction, input_complex_axis, d_in, d_out, stream))
+
+
+def selftest_wait_timeout(limit_cycles: int, pair: bool = False) -> tuple[int, int]:
+    """Make a bounded device-side wait run out (see include/ccglib_b200.h); returns the cycles
+    the two waiters spent.  The device status word is left set."""
+    waited = (ctypes.c_longlong * 2)()
+    _check(lib().ccglib_b200_selftest_wait_timeout(limit_cycles, 1 if pair else 0,
+                                                   ctypes.byref(waited)))
+    return int(waited[0]), int(waited[1])
 
 
 def device_status() -> int:

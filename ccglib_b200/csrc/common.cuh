@@ -46,8 +46,26 @@ int sm_count();
 int launch_expand_bits(const void *d_in, void *d_out, size_t batch, size_t rows, size_t k_bits,
                        size_t out_row_bytes, int planes_out, bool tiled, size_t blk, size_t k_c_bits,
                        cudaStream_t stream, bool nibbles = false);
+// One-byte samples (non-zero = +1) in planar [batch][2][rows][k] or interleaved
+// [batch][rows][k][2] order -> the operand planes of the 1-bit GEMM (see staging.cu).
+int launch_expand_bytes(const void *d_in, void *d_out, size_t batch, size_t rows, size_t k,
+                        size_t out_row_bytes, int planes_out, bool interleaved, cudaStream_t stream,
+                        bool nibbles);
 int launch_pad_rows(const void *d_in, void *d_out, size_t rows, size_t row_bytes,
                     size_t out_row_bytes, cudaStream_t stream);
+
+// Input forms the public GEMM description cannot express; used by the Pipeline.
+struct PlanOptions {
+  bool int1_bytes_in = false;           // 1-bit A and B arrive as one byte per sample
+  bool int1_bytes_interleaved = false;  // ... in [batch][rows][K][2] order (else [batch][2][rows][K])
+};
+
+// ccglib_b200_gemm_plan_create with options; ccglib_b200_gemm_run on the first `items` batch
+// items of a plan (items <= the plan's batch).
+int create_gemm_plan(const ccglib_b200_gemm_desc *desc, const PlanOptions &opt,
+                     ccglib_b200_gemm_plan **out);
+int run_gemm_items(ccglib_b200_gemm_plan *plan, const void *d_a, const void *d_b, void *d_c,
+                   size_t items, void *stream);
 
 } // namespace ccglib_b200
 #endif

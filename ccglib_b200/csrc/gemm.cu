@@ -126,6 +126,14 @@ int env_int(const char *name, int fallback) {
   return (v != nullptr && *v != '\0') ? std::atoi(v) : fallback;
 }
 
+// Limit of the device-side waits in SM clock cycles: CCGLIB_B200_WAIT_CYCLES, else about two
+// seconds.  Never unbounded: values below 1 fall back to the default.
+long long wait_limit_cycles() {
+  const char *v = std::getenv("CCGLIB_B200_WAIT_CYCLES");
+  const long long n = (v != nullptr && *v != '\0') ? std::atoll(v) : 0;
+  return n > 0 ? n : kWaitLimitCycles;
+}
+
 size_t type_bits(int t) {
   switch (t) {
   case CCGLIB_B200_INT1:
@@ -167,6 +175,8 @@ struct ccglib_b200_gemm_plan {
   int bn, sw, a_planes;
   int max_clusters;       // CTA-pair kernels: co-resident clusters of two
   int nibbles;            // 1-bit input expanded to e2m1 nibbles (block-scaled 4-bit MMA path)
+  int bytes_in;           // 1-bit input arrives as one byte per sample (Pipeline), not packed words
+  int bytes_interleaved;  // ... in [batch][rows][K][2] order
   int stage_mode;
   size_t k_bytes;         // bytes per operand row as the kernel reads it (before any padding)
   size_t pitch;           // row pitch in bytes of what the kernel reads (basic layout)
@@ -185,6 +195,7 @@ struct ccglib_b200_gemm_plan {
   uint32_t idesc, idesc_neg_a;
   int device;
   int sms;
+  long long wait_cycles;  // limit of every device-side wait of this plan's kernels
   // per-plan caches: the status word's device address and the tensor maps of the last operands
   mutable unsigned int *status_ptr;
   mutable const void *map_a, *map_b;
@@ -228,6 +239,11 @@ extern "C" int ccglib_b200_gemm_dims(int type_in, int type_out, int variant, uns
 
 extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
                                             ccglib_b200_gemm_plan **out) {
+  return create_gemm_plan(desc, PlanOptions{}, out);
+}
+
+int ccglib_b200::create_gemm_plan(const ccglib_b200_gemm_desc *desc, const PlanOptions &opt,
+                                  ccglib_b200_gemm_plan **out) {
   if (desc == nullptr || out == nullptr) {
     set_last_error("gemm_plan_create: null argument");
     return CCGLIB_B200_INVALID_ARGUMENT;
@@ -247,7 +263,8 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
     set_last_error("gemm_plan_create: unknown variant %d", d.variant);
     return CCGLIB_B200_INVALID_ARGUMENT;
   }
-  if (d.variant == CCGLIB_B200_BASIC && d.c_complex_axis == CCGLIB_B200_INTERLEAVED) {
+  if (d.variant == CCGLIB_B200_BASIC && d.c_complex_axis == CCGLIB_B200_INTERLEAVED &&
+      !opt.int1_bytes_in) {
     set_last_error("complex-interleaved output is not supported in basic variant");
     return CCGLIB_B200_UNSUPPORTED;
   }
@@ -259,9 +276,15 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
     set_last_error("GEMM does not support row-major B matrix");
     return CCGLIB_B200_UNSUPPORTED;
   }
+  if (opt.int1_bytes_in && d.type_in != CCGLIB_B200_INT1) {
+    set_last_error("gemm_plan_create: one-byte samples are a 1-bit input form");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
 
   ccglib_b200_gemm_plan plan{};
   plan.desc = d;
+  plan.bytes_in = opt.int1_bytes_in ? 1 : 0;
+  plan.bytes_interleaved = opt.int1_bytes_interleaved ? 1 : 0;
   CCGLIB_CUDA_TRY(cudaGetDevice(&plan.device));
   plan.sms = sm_count();
   if (plan.sms <= 0) return CCGLIB_B200_CUDA_ERROR;
@@ -271,6 +294,7 @@ extern "C" int ccglib_b200_gemm_plan_create(const ccglib_b200_gemm_desc *desc,
     set_last_error("This architecture is not supported (need compute capability 10.x)");
     return CCGLIB_B200_UNSUPPORTED;
   }
+  plan.wait_cycles = wait_limit_cycles();
 
   // ---- kernel family and instruction descriptor
   // idesc: [4,6) D format, [7,10) A format, [10,13) B format, bit 13 negate A, bit 15/16 majors
@@ -679,6 +703,7 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
     return cuda_fail(cudaGetLastError(), "cudaGetSymbolAddress(g_device_status)");
   }
   p.status = plan.status_ptr;
+  p.wait_cycles = plan.wait_cycles;
   if (pair) {
     const size_t clusters = tiles < static_cast<size_t>(plan.max_clusters)
                                 ? tiles
@@ -709,8 +734,18 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
 int stage_chunk(const ccglib_b200_gemm_plan &plan, const void *d_a, const void *d_b, size_t b0,
                 size_t nb, void *sa, void *sb, cudaStream_t stream) {
   const ccglib_b200_gemm_desc &d = plan.desc;
-  const bool tiled_in = d.variant == CCGLIB_B200_OPT;
+  const bool tiled_in = d.variant == CCGLIB_B200_OPT && !plan.bytes_in;
   int rc;
+  if (plan.stage_mode == kExpandBits && plan.bytes_in) {
+    // one byte per sample, 2 * rows * K bytes per batch item in either complex order
+    rc = launch_expand_bytes(static_cast<const char *>(d_a) + b0 * 2 * d.m * d.k, sa, nb, d.m, d.k,
+                             plan.pitch, plan.a_planes, plan.bytes_interleaved != 0, stream,
+                             plan.nibbles != 0);
+    if (rc != CCGLIB_B200_OK) return rc;
+    return launch_expand_bytes(static_cast<const char *>(d_b) + b0 * 2 * d.n * d.k, sb, nb, d.n,
+                               d.k, plan.pitch, 2, plan.bytes_interleaved != 0, stream,
+                               plan.nibbles != 0);
+  }
   if (plan.stage_mode == kExpandBits) {
     const size_t words = ceil_div<size_t>(d.k, 32);
     size_t a_item, b_item;
@@ -742,13 +777,29 @@ int stage_chunk(const ccglib_b200_gemm_plan &plan, const void *d_a, const void *
 
 extern "C" int ccglib_b200_gemm_run(ccglib_b200_gemm_plan *plan, const void *d_a, const void *d_b,
                                     void *d_c, void *stream_v) {
+  if (plan == nullptr) {
+    set_last_error("gemm_run: null argument");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  return run_gemm_items(plan, d_a, d_b, d_c, plan->desc.batch, stream_v);
+}
+
+int ccglib_b200::run_gemm_items(ccglib_b200_gemm_plan *plan, const void *d_a, const void *d_b,
+                                void *d_c, size_t items, void *stream_v) {
   if (plan == nullptr || d_a == nullptr || d_b == nullptr || d_c == nullptr) {
     set_last_error("gemm_run: null argument");
     return CCGLIB_B200_INVALID_ARGUMENT;
   }
+  if (items == 0 || items > plan->desc.batch) {
+    set_last_error("gemm_run: %zu batch items asked of a plan made for %zu", items,
+                   plan->desc.batch);
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  const ccglib_b200_gemm_desc &d = plan->desc;
-  const bool tiled_in = d.variant == CCGLIB_B200_OPT;
+  // the first `items` batch items: the batch is the outermost axis of every operand
+  ccglib_b200_gemm_desc d = plan->desc;
+  d.batch = items;
+  const bool tiled_in = d.variant == CCGLIB_B200_OPT && !plan->bytes_in;
   if (plan->stage_mode == kDirect) {
     if (!aligned16(d_a) || !aligned16(d_b)) {
       set_last_error("gemm_run: A and B must be 16-byte aligned");
@@ -814,6 +865,87 @@ extern "C" int ccglib_b200_device_status(unsigned *word) {
   return value == 0 ? CCGLIB_B200_OK : CCGLIB_B200_DEVICE_TIMEOUT;
 }
 
+// ------------------------------------------------------------------------------------------
+// Self-test of the time-out machinery: a wait that is guaranteed to run out, made on the host
+// side of the contract (an mbarrier nobody arrives on), so that nothing faults or hangs.
+namespace ccglib_b200 {
+namespace {
+
+__device__ long long g_selftest_waited[2];
+
+// Warp 0 of CTA 0 (the cluster leader in the pair form) waits `limit` cycles on a barrier that
+// never completes, with the same mbar_wait the GEMM kernels use; it must give up, raise the
+// abort flag (its own and, in a pair, the peer's) and record kDevTimeoutProducer.  The second
+// waiter (warp 1 of the same CTA, or warp 0 of the peer CTA) has a limit `other_limit` that is
+// much longer and a different code: it must come back early through the abort flag, without
+// recording its code.  Each waiter stores the cycles it spent.
+template <bool PAIR>
+__global__ void __launch_bounds__(64, 1)
+wait_timeout_selftest_kernel(unsigned int *status, long long limit, long long other_limit) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_word;
+  volatile int *abort_flag = &abort_word;
+  const uint32_t warp = threadIdx.x >> 5;
+  uint32_t rank = 0, peer_abort = 0;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if constexpr (PAIR) {
+    rank = cluster_ctarank();
+    cluster_sync();
+    peer_abort = map_to_cta(smem_u32(&abort_word), rank ^ 1u);
+  } else {
+    __syncthreads();
+  }
+  const bool first = rank == 0 && warp == 0;
+  const bool second = PAIR ? (rank == 1 && warp == 0) : (warp == 1);
+  if (first || second) {
+    const long long t0 = clock64();
+    mbar_wait(smem_u32(&bar), 0, abort_flag, status,
+              first ? kDevTimeoutProducer : kDevTimeoutEpilogue, first ? limit : other_limit,
+              first ? peer_abort : 0u);
+    if ((threadIdx.x & 31) == 0) g_selftest_waited[first ? 0 : 1] = clock64() - t0;
+  }
+  if constexpr (PAIR) {
+    cluster_sync();
+  }
+}
+
+} // namespace
+} // namespace ccglib_b200
+
+extern "C" int ccglib_b200_selftest_wait_timeout(long long limit_cycles, int pair,
+                                                 long long waited_cycles[2]) {
+  if (limit_cycles < 1 || limit_cycles > 10000000ll || waited_cycles == nullptr) {
+    set_last_error("selftest_wait_timeout: limit must be 1..1e7 cycles and the result array non-null");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  unsigned int *status = nullptr;
+  CCGLIB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void **>(&status), g_device_status));
+  const long long other_limit = 200 * limit_cycles;  // bounded as well: at most 2e9 cycles
+  if (pair != 0) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2);
+    cfg.blockDim = dim3(64);
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    CCGLIB_CUDA_TRY(cudaLaunchKernelEx(&cfg, wait_timeout_selftest_kernel<true>, status,
+                                       limit_cycles, other_limit));
+  } else {
+    wait_timeout_selftest_kernel<false><<<1, 64>>>(status, limit_cycles, other_limit);
+    CCGLIB_CUDA_TRY(cudaGetLastError());
+  }
+  CCGLIB_CUDA_TRY(cudaDeviceSynchronize());
+  CCGLIB_CUDA_TRY(cudaMemcpyFromSymbol(waited_cycles, g_selftest_waited, 2 * sizeof(long long)));
+  return CCGLIB_B200_OK;
+}
 
 // ------------------------------------------------------------------------------------------
 // Allocation-free 1-bit GEMM.
@@ -894,6 +1026,7 @@ extern "C" int ccglib_b200_gemm_int1_static_scratch(const ccglib_b200_gemm_desc 
   plan.k_bytes = d.k;
   plan.pitch = ceil_div<size_t>(d.k, 16) * 16;
   plan.out_elem_bytes = 4;
+  plan.wait_cycles = wait_limit_cycles();
   const size_t per_item_a = 3 * d.m * plan.pitch;
   const size_t per_item_b = 2 * d.n * plan.pitch;
   if (per_item_a + per_item_b > kStaticScratchBytes) {

@@ -42,7 +42,7 @@ constexpr int kBlockM = 128;       // rows of A per tile = TMEM lanes
 constexpr int kThreads = 192;      // producer warp, MMA warp, four epilogue warps
 constexpr int kTmemCols = 512;     // whole tensor memory of the SM
 constexpr int kMaxSmem = 227 * 1024;
-constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at boost clock
+constexpr long long kWaitLimitCycles = 4000000000ll;  // default wait limit: ~2 s at boost clock
 
 enum CLayout { kPlanarRow = 0, kPlanarCol = 1, kInterRow = 2, kInterCol = 3 };
 
@@ -67,6 +67,7 @@ struct GemmParams {
   uint32_t prefetch;  // k-blocks the producer asks L2 to fetch ahead of its own loads (0 = off)
   float alpha_re, alpha_im, beta_re, beta_im;
   unsigned int *status;
+  long long wait_cycles;  // SM clock cycles after which a wait on an mbarrier gives up
 };
 
 constexpr int kStagingTile = 32 * 128;  // one staging tile: 32 rows x 128 B
@@ -89,17 +90,22 @@ template <int BN, int SW, int A_PLANES, int EPI> struct Cfg {
 };
 
 // Bounded wait on an mbarrier phase.  Returns false when the abort flag is up or the wait ran out
-// (in which case it raises the flag and records `code`).
+// after `limit` cycles (in which case it raises the flag and records `code`).  In a CTA pair
+// `peer_abort` is the shared::cluster address of the other CTA's abort flag (0: none): the CTA
+// that gives up raises it too, so the pair stops together instead of each role of the peer sitting
+// out its own full limit.  The peer cannot have left: both CTAs meet at the closing cluster barrier.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          unsigned int *status, unsigned code) {
+                                          unsigned int *status, unsigned code, long long limit,
+                                          uint32_t peer_abort = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 0xFFu) == 0) {
+    if ((spin & 0x3Fu) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit) {
         *abort_flag = 1;
+        if (peer_abort != 0) st_shared_cluster_u32(peer_abort, 1u);
         atomicOr(status, code);
         return false;
       }
@@ -518,7 +524,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       const TileCoord t = decode_tile(p, tile);
       for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
         if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status,
-                       kDevTimeoutProducer)) {
+                       kDevTimeoutProducer, p.wait_cycles)) {
           ok = false;
           break;
         }
@@ -549,7 +555,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         const uint32_t last_parity = (static_cast<uint32_t>(s) < stage) ? phase : (phase ^ 1);
         const long long t0 = clock64();
         while (!mbar_try_wait(bar_full + 8 * s, last_parity)) {
-          if (clock64() - t0 > kWaitLimitCycles) {
+          if (clock64() - t0 > p.wait_cycles) {
             atomicOr(p.status, kDevTimeoutDrain);
             break;
           }
@@ -562,14 +568,15 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     bool ok = true;
     for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
       if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1, abort_flag, p.status,
-                     kDevTimeoutMma)) {
+                     kDevTimeoutMma, p.wait_cycles)) {
         break;
       }
       tc_fence_after();
       const uint32_t d_re = tmem_base + acc * (2 * BN);
       const uint32_t d_im = d_re + BN;
       for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
-        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kDevTimeoutMma)) {
+        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kDevTimeoutMma,
+                       p.wait_cycles)) {
           ok = false;
           break;
         }
@@ -630,7 +637,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     for (uint32_t tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
       const TileCoord t = decode_tile(p, tile);
       if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, p.status,
-                     kDevTimeoutEpilogue)) {
+                     kDevTimeoutEpilogue, p.wait_cycles)) {
         break;
       }
       tc_fence_after();
@@ -742,6 +749,7 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const uint32_t pair = cluster_id_x();
   const uint32_t num_pairs = cluster_count_x();
+  const uint32_t peer_abort = map_to_cta(smem_u32(const_cast<int *>(abort_flag)), rank ^ 1u);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -789,7 +797,7 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       const uint32_t mt = t.mt * 2 + rank;  // this CTA's 128-row block
       for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
         if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status,
-                       kDevTimeoutProducer)) {
+                       kDevTimeoutProducer, p.wait_cycles)) {
           ok = false;
           break;
         }
@@ -835,7 +843,7 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         const uint32_t last_parity = (static_cast<uint32_t>(s) < stage) ? phase : (phase ^ 1);
         const long long t0 = clock64();
         while (!mbar_try_wait(bar_full + 8 * s, last_parity)) {
-          if (clock64() - t0 > kWaitLimitCycles) {
+          if (clock64() - t0 > p.wait_cycles) {
             atomicOr(p.status, kDevTimeoutDrain);
             break;
           }
@@ -849,14 +857,15 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       bool ok = true;
       for (uint32_t tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
         if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1, abort_flag, p.status,
-                       kDevTimeoutMma)) {
+                       kDevTimeoutMma, p.wait_cycles, peer_abort)) {
           break;
         }
         tc_fence_after();
         const uint32_t d_re = tmem_base + acc * (2 * BN);
         const uint32_t d_im = d_re + BN;
         for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kDevTimeoutMma)) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kDevTimeoutMma,
+                       p.wait_cycles)) {
             ok = false;
             break;
           }
@@ -922,7 +931,7 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
     for (uint32_t tile = pair; tile < p.num_tiles; tile += num_pairs) {
       const TileCoord t = decode_tile(p, tile);
       if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, p.status,
-                     kDevTimeoutEpilogue)) {
+                     kDevTimeoutEpilogue, p.wait_cycles)) {
         break;
       }
       tc_fence_after();

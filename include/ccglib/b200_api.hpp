@@ -23,7 +23,6 @@
 #include <climits>
 #include <complex>
 #include <cstddef>
-#include <memory>
 #include <stdexcept>
 #include <string>
 
@@ -115,23 +114,6 @@ inline void check(CUresult result, const char *what) {
 
 inline void *ptr(CUdeviceptr p) { return reinterpret_cast<void *>(p); }
 
-// Device allocation owned by an object (Pipeline scratch).
-class DeviceBuffer {
-public:
-  explicit DeviceBuffer(size_t bytes) : bytes_(bytes) {
-    check(cuMemAlloc(&ptr_, bytes ? bytes : 1), "cuMemAlloc");
-  }
-  ~DeviceBuffer() { cuMemFree(ptr_); }
-  DeviceBuffer(const DeviceBuffer &) = delete;
-  DeviceBuffer &operator=(const DeviceBuffer &) = delete;
-  CUdeviceptr get() const { return ptr_; }
-  size_t size() const { return bytes_; }
-
-private:
-  CUdeviceptr ptr_ = 0;
-  size_t bytes_;
-};
-
 } // namespace detail
 
 // ---- GEMM ---------------------------------------------------------------------------------------
@@ -160,6 +142,9 @@ public:
     detail::check(ccglib_b200_gemm_run(plan_, detail::ptr(d_a), detail::ptr(d_b),
                                        detail::ptr(d_c), stream_));
   }
+
+  // The stream this object enqueues on (the handle given at construction).
+  CUstream stream() const { return stream_; }
 
   // (m_per_block, n_per_block, k_per_chunk) of the tiled layout the opt variant reads.
   static dim3 GetDimensions(Precision precision, Variant variant = Variant::opt) {
@@ -245,6 +230,9 @@ public:
     detail::check(cuMemFreeAsync(tmp, stream_), "cuMemFreeAsync");
   }
 
+  // The stream this object enqueues on (the handle given at construction).
+  CUstream stream() const { return stream_; }
+
   // Bytes of the input array ([B][2][M][N] elements of nr_bits each).
   size_t InputBytes() const { return B_ * 2 * M_ * N_ * nr_bits_ / CHAR_BIT; }
   // Bytes of the zero-padded tiled output.
@@ -288,13 +276,7 @@ class Packing {
 public:
   Packing(size_t N, Direction direction, CUdevice &device, CUstream &stream,
           ComplexAxisLocation input_complex_axis_location = ComplexAxisLocation::complex_planar)
-      : N_(N), direction_(direction), axis_(input_complex_axis_location), stream_(stream) {
-    (void)device;
-    if (direction == Direction::backward &&
-        input_complex_axis_location == ComplexAxisLocation::complex_interleaved) {
-      throw std::runtime_error("complex-interleaved input is not supported in unpacking kernel");
-    }
-  }
+      : Packing(FromHandles{}, N, direction, device, stream, input_complex_axis_location) {}
 
   void Run(CUdeviceptr d_input, CUdeviceptr d_output) {
     detail::check(ccglib_b200_pack_run(N_, direction_, axis_, detail::ptr(d_input),
@@ -314,8 +296,8 @@ public:
 #ifdef CCGLIB_B200_HAVE_CUDAWRAPPERS
   Packing(size_t N, Direction direction, cu::Device &device, cu::Stream &stream,
           ComplexAxisLocation input_complex_axis_location = ComplexAxisLocation::complex_planar)
-      : Packing(N, direction, raw_device(device), raw_stream(stream),
-                input_complex_axis_location) {}
+      : Packing(FromHandles{}, N, direction, static_cast<CUdevice>(device),
+                static_cast<CUstream>(stream), input_complex_axis_location) {}
   void Run(cu::HostMemory &h_input, cu::DeviceMemory &d_output) {
     Run(static_cast<unsigned char *>(static_cast<void *>(h_input)),
         static_cast<CUdeviceptr>(d_output));
@@ -325,13 +307,23 @@ public:
   }
 #endif
 
+  // The stream this object enqueues on (the handle given at construction).
+  CUstream stream() const { return stream_; }
+
 private:
-#ifdef CCGLIB_B200_HAVE_CUDAWRAPPERS
-  CUdevice tmp_device_{};
-  CUstream tmp_stream_{};
-  CUdevice &raw_device(cu::Device &d) { return tmp_device_ = static_cast<CUdevice>(d); }
-  CUstream &raw_stream(cu::Stream &s) { return tmp_stream_ = static_cast<CUstream>(s); }
-#endif
+  // Both public constructors delegate here with the raw handles taken BY VALUE, so the stored
+  // stream is the caller's whichever overload was used.
+  struct FromHandles {};
+  Packing(FromHandles, size_t N, Direction direction, CUdevice device, CUstream stream,
+          ComplexAxisLocation input_complex_axis_location)
+      : N_(N), direction_(direction), axis_(input_complex_axis_location), stream_(stream) {
+    (void)device;
+    if (direction == Direction::backward &&
+        input_complex_axis_location == ComplexAxisLocation::complex_interleaved) {
+      throw std::runtime_error("complex-interleaved input is not supported in unpacking kernel");
+    }
+  }
+
   size_t N_;
   Direction direction_;
   ComplexAxisLocation axis_;
@@ -344,8 +336,11 @@ private:
 
 namespace pipeline {
 
-// pack (1-bit input only) -> transpose (opt variant only) -> gemm on one stream; owns the packed
-// and tiled scratch buffers, allocated once at construction.
+// The caller's matrices in their natural layout -> C: for floating-point input transpose (opt
+// variant only) -> gemm; for 1-bit input, given as one byte per sample, the GEMM's own front end
+// turns the bytes into tensor-core operands, so nothing is packed or tiled first.  The object
+// owns the intermediate buffers (allocated once at construction; the device slices of the
+// host-memory Run at its first call).
 class Pipeline {
 public:
   Pipeline(size_t B, size_t M, size_t N, size_t K, CUdevice &device, CUstream &stream,
@@ -354,75 +349,29 @@ public:
            mma::MemOrder b_mem_order, mma::MemOrder c_mem_order, ValuePrecision input_precision,
            ValuePrecision output_precision, mma::Variant variant = mma::Variant::opt,
            std::complex<float> alpha = {1, 0}, std::complex<float> beta = {0, 0})
-      : need_copyin_c_(beta.real() != 0 || beta.imag() != 0), stream_(stream) {
-    const bool packs = input_precision == int1;
-    // 1-bit operands are re-staged by the GEMM itself whatever their layout, so tiling them first
-    // would only add a pass over memory: with planar output (the only kind the basic variant
-    // writes) the pipeline hands the packed words over as they are
-    if (packs && output_complex_axis_location == complex_planar) variant = mma::basic;
-    const bool tiles = variant == mma::opt;
-    const Precision precision(input_precision, output_precision);
-    const size_t bits = precision.GetInputBits();
-    const size_t num_a = B * 2 * M * K;
-    const size_t num_b = B * 2 * N * K;
-    bytes_a_ = packs ? num_a : num_a * bits / CHAR_BIT;  // what the caller passes in
-    bytes_b_ = packs ? num_b : num_b * bits / CHAR_BIT;
-    bytes_c_ = B * 2 * M * N * precision.GetOutputBits() / CHAR_BIT;
-    if (packs) {
-      pack_a_ = std::make_unique<packing::Packing>(num_a, forward, device, stream,
-                                                  input_complex_axis_location);
-      pack_b_ = std::make_unique<packing::Packing>(num_b, forward, device, stream,
-                                                  input_complex_axis_location);
-      packed_a_ = std::make_unique<detail::DeviceBuffer>(4 * helper::ceildiv(num_a, size_t{32}));
-      packed_b_ = std::make_unique<detail::DeviceBuffer>(4 * helper::ceildiv(num_b, size_t{32}));
-    }
-    if (tiles) {
-      const dim3 dims = mma::GEMM::GetDimensions(precision, variant);
-      // after packing the samples are planar whatever the caller's layout was
-      const ComplexAxisLocation axis = packs ? complex_planar : input_complex_axis_location;
-      trans_a_ = std::make_unique<transpose::Transpose>(B, M, K, dims.x, dims.z, bits, device,
-                                                       stream, axis);
-      trans_b_ = std::make_unique<transpose::Transpose>(B, N, K, dims.y, dims.z, bits, device,
-                                                       stream, axis);
-      tiled_a_ = std::make_unique<detail::DeviceBuffer>(trans_a_->OutputBytes());
-      tiled_b_ = std::make_unique<detail::DeviceBuffer>(trans_b_->OutputBytes());
-    }
-    gemm_ = std::make_unique<mma::GEMM>(B, M, N, K, device, stream, precision, variant,
-                                        output_complex_axis_location, c_mem_order, a_mem_order,
-                                        b_mem_order, alpha, beta);
+      : stream_(stream) {
+    (void)device;  // the current context's device is used, as with the reference
+    create(B, M, N, K, input_complex_axis_location, output_complex_axis_location, a_mem_order,
+           b_mem_order, c_mem_order, input_precision, output_precision, variant, alpha, beta);
   }
+  ~Pipeline() { ccglib_b200_pipeline_destroy(pipeline_); }
+  Pipeline(const Pipeline &) = delete;
+  Pipeline &operator=(const Pipeline &) = delete;
 
-  // Device operands: asynchronous, no allocation.
+  // Device operands: asynchronous on the stream given at construction, no allocation.
   void Run(CUdeviceptr d_a, CUdeviceptr d_b, CUdeviceptr d_c) {
-    if (pack_a_) {
-      pack_a_->Run(d_a, packed_a_->get());
-      pack_b_->Run(d_b, packed_b_->get());
-      d_a = packed_a_->get();
-      d_b = packed_b_->get();
-    }
-    if (trans_a_) {
-      trans_a_->Run(d_a, tiled_a_->get());
-      trans_b_->Run(d_b, tiled_b_->get());
-      d_a = tiled_a_->get();
-      d_b = tiled_b_->get();
-    }
-    gemm_->Run(d_a, d_b, d_c);
+    detail::check(ccglib_b200_pipeline_run(pipeline_, detail::ptr(d_a), detail::ptr(d_b),
+                                           detail::ptr(d_c), stream_));
   }
 
-  // Host operands: allocates device copies, runs, copies C back and synchronises the stream.
+  // Host operands: batch slices are copied in, run and copied back double-buffered; returns when
+  // C is complete in host memory (as the reference's host-memory Run, which synchronises too).
   void RunHost(const void *a, const void *b, void *c) {
-    detail::DeviceBuffer d_a(bytes_a_), d_b(bytes_b_), d_c(bytes_c_);
-    detail::check(cuMemcpyHtoDAsync(d_a.get(), a, bytes_a_, stream_), "cuMemcpyHtoDAsync");
-    detail::check(cuMemcpyHtoDAsync(d_b.get(), b, bytes_b_, stream_), "cuMemcpyHtoDAsync");
-    if (need_copyin_c_) {
-      detail::check(cuMemcpyHtoDAsync(d_c.get(), c, bytes_c_, stream_), "cuMemcpyHtoDAsync");
-    } else {
-      detail::check(cuMemsetD8Async(d_c.get(), 0, bytes_c_, stream_), "cuMemsetD8Async");
-    }
-    Run(d_a.get(), d_b.get(), d_c.get());
-    detail::check(cuMemcpyDtoHAsync(c, d_c.get(), bytes_c_, stream_), "cuMemcpyDtoHAsync");
-    detail::check(cuStreamSynchronize(stream_), "cuStreamSynchronize");
+    detail::check(ccglib_b200_pipeline_run_host(pipeline_, a, b, c, stream_));
   }
+
+  // The stream this object enqueues on (the handle given at construction).
+  CUstream stream() const { return stream_; }
 
 #ifdef CCGLIB_B200_HAVE_CUDAWRAPPERS
   Pipeline(size_t B, size_t M, size_t N, size_t K, cu::Device &device, cu::Stream &stream,
@@ -431,9 +380,11 @@ public:
            mma::MemOrder b_mem_order, mma::MemOrder c_mem_order, ValuePrecision input_precision,
            ValuePrecision output_precision, mma::Variant variant = mma::Variant::opt,
            std::complex<float> alpha = {1, 0}, std::complex<float> beta = {0, 0})
-      : Pipeline(B, M, N, K, raw_device(device), raw_stream(stream), input_complex_axis_location,
-                 output_complex_axis_location, a_mem_order, b_mem_order, c_mem_order,
-                 input_precision, output_precision, variant, alpha, beta) {}
+      : stream_(static_cast<CUstream>(stream)) {
+    (void)device;
+    create(B, M, N, K, input_complex_axis_location, output_complex_axis_location, a_mem_order,
+           b_mem_order, c_mem_order, input_precision, output_precision, variant, alpha, beta);
+  }
   void Run(cu::HostMemory &a, cu::HostMemory &b, cu::HostMemory &c) {
     RunHost(static_cast<void *>(a), static_cast<void *>(b), static_cast<void *>(c));
   }
@@ -444,19 +395,32 @@ public:
 #endif
 
 private:
-#ifdef CCGLIB_B200_HAVE_CUDAWRAPPERS
-  CUdevice tmp_device_{};
-  CUstream tmp_stream_{};
-  CUdevice &raw_device(cu::Device &d) { return tmp_device_ = static_cast<CUdevice>(d); }
-  CUstream &raw_stream(cu::Stream &s) { return tmp_stream_ = static_cast<CUstream>(s); }
-#endif
-  const bool need_copyin_c_;
+  void create(size_t B, size_t M, size_t N, size_t K, ComplexAxisLocation in_axis,
+              ComplexAxisLocation out_axis, mma::MemOrder a_order, mma::MemOrder b_order,
+              mma::MemOrder c_order, ValuePrecision in, ValuePrecision out, mma::Variant variant,
+              std::complex<float> alpha, std::complex<float> beta) {
+    ccglib_b200_pipeline_desc d{};
+    d.batch = B;
+    d.m = M;
+    d.n = N;
+    d.k = K;
+    d.type_in = static_cast<ValueType>(in);
+    d.type_out = static_cast<ValueType>(out);
+    d.variant = variant;
+    d.input_complex_axis = in_axis;
+    d.output_complex_axis = out_axis;
+    d.a_mem_order = a_order;
+    d.b_mem_order = b_order;
+    d.c_mem_order = c_order;
+    d.alpha_re = alpha.real();
+    d.alpha_im = alpha.imag();
+    d.beta_re = beta.real();
+    d.beta_im = beta.imag();
+    detail::check(ccglib_b200_pipeline_create(&d, &pipeline_));
+  }
+
+  ccglib_b200_pipeline *pipeline_ = nullptr;
   CUstream stream_;
-  size_t bytes_a_ = 0, bytes_b_ = 0, bytes_c_ = 0;
-  std::unique_ptr<packing::Packing> pack_a_, pack_b_;
-  std::unique_ptr<transpose::Transpose> trans_a_, trans_b_;
-  std::unique_ptr<detail::DeviceBuffer> packed_a_, packed_b_, tiled_a_, tiled_b_;
-  std::unique_ptr<mma::GEMM> gemm_;
 };
 
 } // namespace pipeline

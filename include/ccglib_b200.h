@@ -140,6 +140,76 @@ CCGLIB_B200_API int ccglib_b200_pack_run(size_t n, int direction, int input_comp
                          void *d_out, void *stream);
 
 /*
+ * The Pipeline: the caller's matrices in their natural layout -> C, as one object that owns the
+ * intermediate buffers.  Replaces ccglib::pipeline::Pipeline (reference
+ * include/ccglib/pipeline/pipeline.h:28-73, src/pipeline/Pipeline.cpp:44-188), whose chain is
+ * Packing (1-bit input) -> Transpose (opt variant) -> GEMM as separate launches.
+ *
+ * Input A: [batch][2][M][K] (planar) or [batch][M][K][2] (interleaved) elements of type_in, B
+ * likewise with N rows; 1-bit input is given as ONE BYTE PER SAMPLE (non-zero = +1, zero = -1),
+ * as the reference's Pipeline takes it (src/pipeline/Pipeline.cpp:58-72).  C as for the GEMM.
+ *   - floating point, opt variant: Transpose A, Transpose B (which also de-interleaves), GEMM.
+ *   - floating point, basic variant: GEMM on the caller's buffers (planar input only).
+ *   - 1-bit: the byte samples are turned into tensor-core operands by the GEMM's own front end,
+ *     chunk by chunk; no packed or tiled copy of A and B is ever written, whatever the variant,
+ *     and interleaved C is available with either variant.  Interleaved 1-bit input is
+ *     de-interleaved per batch item (the reference's packing pass treats the whole buffer as one
+ *     [n/2][2] array, kernels/packing_kernel.cu:15-22, which is the same thing for batch 1).
+ */
+typedef struct ccglib_b200_pipeline_desc {
+  size_t batch;
+  size_t m;
+  size_t n;
+  size_t k;
+  int type_in;
+  int type_out;
+  int variant;
+  int input_complex_axis;
+  int output_complex_axis;
+  int a_mem_order; /* must be row-major */
+  int b_mem_order; /* must be col-major */
+  int c_mem_order;
+  float alpha_re, alpha_im;
+  float beta_re, beta_im;
+} ccglib_b200_pipeline_desc;
+
+typedef struct ccglib_b200_pipeline ccglib_b200_pipeline;
+
+/* Validates, creates the GEMM plan and allocates the tiled buffers of the device path.
+ * Replaces Pipeline::Impl::Impl (reference src/pipeline/Pipeline.cpp:44-106). */
+CCGLIB_B200_API int ccglib_b200_pipeline_create(const ccglib_b200_pipeline_desc *desc,
+                                                ccglib_b200_pipeline **pipeline);
+
+/* Device operands: enqueues the chain on `stream`; no allocation, no synchronisation.
+ * Replaces Pipeline::Run(CUdeviceptr a, b, c) (reference src/pipeline/Pipeline.cpp:108-126,178-188). */
+CCGLIB_B200_API int ccglib_b200_pipeline_run(ccglib_b200_pipeline *pipeline, const void *d_a,
+                                             const void *d_b, void *d_c, void *stream);
+
+/* Host operands (whole A, B, C in host memory; pinned memory lets the copies overlap the
+ * kernels, pageable memory works but serialises).  The batch is cut into slices; each slice is
+ * copied in, run through the chain and copied back on three internal streams with two sets of
+ * device slice buffers, so host->device, kernels and device->host of neighbouring slices
+ * overlap.  Ordered after what `stream` holds at the call; returns when C is complete in host
+ * memory.  With beta != 0 the caller's C is copied in first.  The first call allocates the
+ * device slices (kept until destroy).  Replaces Pipeline::Run(cu::HostMemory& a, b, c)
+ * (reference src/pipeline/Pipeline.cpp:162-176: whole-buffer copies, run, copy back,
+ * synchronise). */
+CCGLIB_B200_API int ccglib_b200_pipeline_run_host(ccglib_b200_pipeline *pipeline, const void *h_a,
+                                                  const void *h_b, void *h_c, void *stream);
+
+/* Batch items per slice of the host path: read, or set before the first run_host (default: about
+ * 1 GiB of operands per slice).  No counterpart in the reference. */
+CCGLIB_B200_API size_t ccglib_b200_pipeline_host_slice(const ccglib_b200_pipeline *pipeline);
+CCGLIB_B200_API int ccglib_b200_pipeline_set_host_slice(ccglib_b200_pipeline *pipeline, size_t items);
+
+/* Kernel launches one ccglib_b200_pipeline_run enqueues, and device bytes the pipeline owns.
+ * Introspection for benchmarks; no counterpart in the reference. */
+CCGLIB_B200_API size_t ccglib_b200_pipeline_launches(const ccglib_b200_pipeline *pipeline);
+CCGLIB_B200_API size_t ccglib_b200_pipeline_scratch_bytes(const ccglib_b200_pipeline *pipeline);
+
+CCGLIB_B200_API int ccglib_b200_pipeline_destroy(ccglib_b200_pipeline *pipeline);
+
+/*
  * 1-bit complex GEMM that allocates nothing, for callers that cannot call cudaMalloc: a
  * correlator or beamformer loop whose device memory was handed out in full at start-up (a later
  * allocation would fail), or a host thread that cannot afford the device-wide synchronisation an
@@ -152,7 +222,10 @@ CCGLIB_B200_API int ccglib_b200_pack_run(size_t n, int direction, int input_comp
  *   - Limit: one batch item must fit, (3*M + 2*N) * round_up(K, 16) <= 32 MiB; larger problems
  *     get INVALID_ARGUMENT and should use a plan.  Batches are processed in chunks that fit.
  *   - The first call on each device looks up the array's device address (with that device
- *     current); make that first call before starting any stream capture on that device.
+ *     current); make that first call before starting any stream capture on that device.  With
+ *     CUDA's default lazy module loading the part of the library image that holds the array is
+ *     loaded by the first call into the GEMM code, so a process whose very first library call is
+ *     this one also pays that module load (and the 32 MiB) there.
  *   - All calls on a device share the one array and it keeps the last call's contents.  Nothing
  *     has to be cleared: each call rewrites every row it later reads, padding included.  Calls
  *     that can overlap on the GPU (different streams, or threads) race on it; serialise them.
@@ -164,6 +237,18 @@ CCGLIB_B200_API int ccglib_b200_gemm_int1_static_scratch(const ccglib_b200_gemm_
 /* Read and clear the sticky device-side status word of the current device (synchronises the
  * device).  Non-zero means a bounded wait inside a kernel gave up; its results are invalid. */
 CCGLIB_B200_API int ccglib_b200_device_status(unsigned *word);
+
+/* Self-test of the bounded device-side waits; no counterpart in the reference (its kernels
+ * have no waits that can run out).  Launches a tiny kernel on the default stream in which one
+ * waiter waits `limit_cycles` (1..1e7 SM clock cycles) on a barrier nobody arrives on, with the
+ * same wait routine the GEMM kernels use, and a second waiter (another warp when pair == 0, the
+ * other CTA of a two-CTA cluster when pair != 0) has a 200 times longer limit.  The first must
+ * give up and set the time-out bit 1 in the device status word; the second must return early
+ * through the abort flag without setting its own bit (4).  Nothing faults or hangs: the wait
+ * simply runs out.  Synchronises the device; waited_cycles[0], [1] receive the cycles each
+ * waiter spent.  The status word is left set: read it with ccglib_b200_device_status. */
+CCGLIB_B200_API int ccglib_b200_selftest_wait_timeout(long long limit_cycles, int pair,
+                                                      long long waited_cycles[2]);
 
 CCGLIB_B200_API const char *ccglib_b200_status_string(int status);
 

@@ -29,7 +29,10 @@ CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 
 def reference_root() -> str:
-    return os.environ.get("CCGLIB_REFERENCE_ROOT", "/root/reference")
+    """Checkout of the reference project: CCGLIB_REFERENCE_ROOT, else a `reference` directory
+    beside this repository.  When neither exists the reference builds are skipped."""
+    return os.environ.get("CCGLIB_REFERENCE_ROOT") or os.path.join(
+        os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def _newer(target: str, sources: list[str]) -> bool:

@@ -18,7 +18,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref", "gpu")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
-REF = os.environ.get("CCGLIB_REFERENCE_ROOT", "/root/reference")
+# checkout of the reference project: CCGLIB_REFERENCE_ROOT, else `reference` beside this repository
+REF = os.environ.get("CCGLIB_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(HERE)), "reference")
 
 # ValueType ordinals (include/ccglib/common/value_type.h:14-22)
 VT = {"int1": 0, "int32": 1, "bf16": 2, "e4m3": 3, "e5m2": 4, "f16": 5, "f32": 6}

@@ -195,6 +195,133 @@ bool pipeline_int1_host() {
   return std::memcmp(static_cast<int *>(h_c), want.data(), want.size() * sizeof(int)) == 0;
 }
 
+// The cu::Stream overloads must enqueue on the CALLER's stream.  A non-blocking stream is not
+// ordered against the NULL stream, so an object that silently fell back to stream 0 would read
+// the device input before the (long) asynchronous copy on the caller's stream has filled it.
+bool packing_on_nonblocking_cu_stream() {
+  cu::init();
+  cu::Device device(0);
+  cu::Context context(CU_CTX_SCHED_BLOCKING_SYNC, device);
+  cu::Stream stream(CU_STREAM_NON_BLOCKING);
+  const size_t N = size_t{96} << 20;  // 96 Mi samples: the copy in takes milliseconds
+  ccglib::packing::Packing pack(N, ccglib::forward, device, stream);
+  if (pack.stream() != static_cast<CUstream>(stream)) return false;  // host-only check
+  cu::HostMemory h_in(N), h_out(N / 8);
+  unsigned char *in = h_in;
+  std::mt19937 rng(21);
+  for (size_t i = 0; i < N; i += 4) {
+    const uint32_t r = rng();
+    in[i] = r & 1, in[i + 1] = (r >> 1) & 1, in[i + 2] = (r >> 2) & 1, in[i + 3] = (r >> 3) & 1;
+  }
+  cu::DeviceMemory d_in(N), d_out(N / 8);
+  cu::checkCudaCall(cuMemsetD8(d_in, 0xFF, N));  // what a racing kernel would read
+  cu::checkCudaCall(cuMemsetD8(d_out, 0, N / 8));
+  cu::checkCudaCall(cuCtxSynchronize());
+  stream.memcpyHtoDAsync(d_in, in, N);
+  pack.Run(d_in, d_out);
+  stream.memcpyDtoHAsync(h_out, d_out, N / 8);
+  stream.synchronize();  // only the caller's stream
+  std::vector<uint32_t> want(N / 32);
+  oracle_pack_bits(in, want.data(), N, 0);
+  return std::memcmp(static_cast<uint32_t *>(h_out), want.data(), N / 8) == 0;
+}
+
+bool pipeline_on_nonblocking_cu_stream() {
+  cu::init();
+  cu::Device device(0);
+  cu::Context context(CU_CTX_SCHED_BLOCKING_SYNC, device);
+  cu::Stream stream(CU_STREAM_NON_BLOCKING);
+  const size_t B = 8, M = 512, N = 512, K = 4096;  // 64 MiB per operand
+  ccglib::pipeline::Pipeline pipeline(B, M, N, K, device, stream, ccglib::complex_planar,
+                                      ccglib::complex_planar, ccglib::mma::row_major,
+                                      ccglib::mma::col_major, ccglib::mma::row_major,
+                                      ccglib::float16, ccglib::float32, ccglib::mma::opt);
+  if (pipeline.stream() != static_cast<CUstream>(stream)) return false;  // host-only check
+  ccglib::mma::GEMM gemm(B, M, N, K, device, stream, ccglib::ValueType::float16);
+  ccglib::transpose::Transpose transpose(B, M, K, 128, 64, 16, device, stream);
+  if (gemm.stream() != static_cast<CUstream>(stream) ||
+      transpose.stream() != static_cast<CUstream>(stream)) {
+    return false;
+  }
+  const size_t na = B * 2 * M * K, nb = B * 2 * N * K, nc = B * 2 * M * N;
+  cu::HostMemory h_a(na * sizeof(half)), h_b(nb * sizeof(half)), h_c(nc * sizeof(float));
+  half *pa = h_a, *pb = h_b;
+  float *pc = h_c;
+  std::mt19937 rng(23);
+  std::uniform_real_distribution<float> dist(-1.0f, 1.0f);
+  for (size_t i = 0; i < na; ++i) pa[i] = __float2half(dist(rng));
+  for (size_t i = 0; i < nb; ++i) pb[i] = __float2half(dist(rng));
+  cu::DeviceMemory d_a(na * sizeof(half)), d_b(nb * sizeof(half)), d_c(nc * sizeof(float));
+  cu::checkCudaCall(cuMemsetD8(d_a, 0, na * sizeof(half)));  // a racing kernel would compute 0
+  cu::checkCudaCall(cuMemsetD8(d_b, 0, nb * sizeof(half)));
+  cu::checkCudaCall(cuCtxSynchronize());
+  stream.memcpyHtoDAsync(d_a, pa, na * sizeof(half));
+  stream.memcpyHtoDAsync(d_b, pb, nb * sizeof(half));
+  pipeline.Run(d_a, d_b, d_c);
+  stream.memcpyDtoHAsync(pc, d_c, nc * sizeof(float));
+  stream.synchronize();  // only the caller's stream
+  // sampled float64 dot products of the same inputs
+  for (int s = 0; s < 4000; ++s) {
+    const size_t b = rng() % B, m = rng() % M, n = rng() % N;
+    double re = 0, im = 0;
+    for (size_t k = 0; k < K; ++k) {
+      const double ar = __half2float(pa[((b * 2) * M + m) * K + k]);
+      const double ai = __half2float(pa[((b * 2 + 1) * M + m) * K + k]);
+      const double br = __half2float(pb[((b * 2) * N + n) * K + k]);
+      const double bi = __half2float(pb[((b * 2 + 1) * N + n) * K + k]);
+      re += ar * br - ai * bi;
+      im += ar * bi + ai * br;
+    }
+    const double tol = 4.0 * std::sqrt(2.0 * K) * 5.96e-8 * K;  // S <= 2K for |values| <= 1
+    if (std::fabs(pc[((b * 2) * M + m) * N + n] - re) > tol ||
+        std::fabs(pc[((b * 2 + 1) * M + m) * N + n] - im) > tol) {
+      return false;
+    }
+  }
+  return true;
+}
+
+bool pipeline_int1_interleaved_in_and_out() {
+  // byte samples [B][M][K][2] in (any non-zero byte = +1), interleaved int32 C [B][M][N][2] out
+  cu::init();
+  cu::Device device(0);
+  cu::Context context(CU_CTX_SCHED_BLOCKING_SYNC, device);
+  cu::Stream stream(CU_STREAM_NON_BLOCKING);
+  const size_t B = 5, M = 200, N = 136, K = 1056;
+  ccglib::pipeline::Pipeline pipeline(B, M, N, K, device, stream, ccglib::complex_interleaved,
+                                      ccglib::complex_interleaved, ccglib::mma::row_major,
+                                      ccglib::mma::col_major, ccglib::mma::row_major, ccglib::int1,
+                                      ccglib::int32, ccglib::mma::basic);
+  cu::HostMemory h_a(B * 2 * M * K), h_b(B * 2 * N * K), h_c(B * 2 * M * N * sizeof(int));
+  std::mt19937 rng(29);
+  unsigned char *pa = h_a, *pb = h_b;
+  for (size_t i = 0; i < h_a.size(); ++i) pa[i] = (rng() & 1) * (1 + rng() % 200);  // non-zero = +1
+  for (size_t i = 0; i < h_b.size(); ++i) pb[i] = rng() & 1;
+  pipeline.Run(h_a, h_b, h_c);
+  // oracle: de-interleave per batch item, pack, multiply
+  std::vector<int32_t> want(2 * M * N);
+  const int *got = h_c;
+  for (size_t bb = 0; bb < B; ++bb) {
+    std::vector<uint8_t> a_pl(2 * M * K), b_pl(2 * N * K);
+    for (size_t r = 0; r < M; ++r)
+      for (size_t k = 0; k < K; ++k)
+        for (size_t c = 0; c < 2; ++c) a_pl[(c * M + r) * K + k] = pa[((bb * M + r) * K + k) * 2 + c];
+    for (size_t r = 0; r < N; ++r)
+      for (size_t k = 0; k < K; ++k)
+        for (size_t c = 0; c < 2; ++c) b_pl[(c * N + r) * K + k] = pb[((bb * N + r) * K + k) * 2 + c];
+    std::vector<uint32_t> wa(2 * M * K / 32), wb(2 * N * K / 32);
+    oracle_pack_bits(a_pl.data(), wa.data(), a_pl.size(), 0);
+    oracle_pack_bits(b_pl.data(), wb.data(), b_pl.size(), 0);
+    std::fill(want.begin(), want.end(), 0);
+    oracle_cgemm_int1(wa.data(), wb.data(), want.data(), M, N, K, 0, 1, 0, 0, 0);
+    for (size_t m = 0; m < M; ++m)
+      for (size_t n = 0; n < N; ++n)
+        for (size_t c = 0; c < 2; ++c)
+          if (got[((bb * M + m) * N + n) * 2 + c] != want[(c * M + m) * N + n]) return false;
+  }
+  return true;
+}
+
 bool transpose_cases(Cuda &cuda) {
   // test/transpose/transpose.cpp:37-46 (B=2, 256 x 128, chunks 64 x 64), host and device input
   const size_t B = 2, M = 256, N = 128, Mc = 64, Nc = 64;
@@ -338,6 +465,10 @@ int main() {
   run_case("pipeline_f16_host_interleaved",
            [] { return pipeline_f16_host(ccglib::complex_interleaved); });
   run_case("pipeline_int1_host", [] { return pipeline_int1_host(); });
+  run_case("packing_on_nonblocking_cu_stream", [] { return packing_on_nonblocking_cu_stream(); });
+  run_case("pipeline_on_nonblocking_cu_stream", [] { return pipeline_on_nonblocking_cu_stream(); });
+  run_case("pipeline_int1_interleaved_in_and_out",
+           [] { return pipeline_int1_interleaved_in_and_out(); });
   run_case("transpose_host_and_device", [&] { return transpose_cases(cuda); });
   run_case("packing_host_and_device", [&] { return packing_cases(cuda); });
   run_case("error_cases_and_dims", [&] { return error_cases(cuda); });

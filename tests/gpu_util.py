@@ -119,26 +119,36 @@ def out_rounding_unit(type_out):
     return {ou.F32: 0.0, ou.INT32: 0.0, ou.F16: 2.0 ** -11, ou.BF16: 2.0 ** -8}[type_out]
 
 
+# Gate on the accumulation error in units of sqrt(2K) * 2^-24 * S.  Measured on this library's
+# kernels: 0.02-0.1 for every input type (fp8 included: the f8f6f4 pipe accumulates in full fp32).
+FP64_GATE_UNITS = 4.0
+
+
 def assert_close_fp64(got, type_in, type_out, a, b, K):
     """Stated tolerance of this library for floating-point types, against a float64 product
     of the same stored inputs (alpha = 1, beta = 0):
 
-        |c - c64| <= 2 * (2K + 2) * 2^-24 * S  +  u_out * |c64|  (+ smallest subnormal)
+        |c - c64| <= 4 * sqrt(2K) * 2^-24 * S  +  2 * u_out * |c64|  (+ smallest subnormal)
 
     S = sum_k |ar||br| + |ai||bi| (imaginary part: |ar||bi| + |ai||br|).  Products of two
     f16 / bf16 / tf32 / fp8 values are exact in float32, so the only error is float32
-    accumulation of 2K terms in tensor-core order, bounded term by term (valid for rounding
-    or truncating adders); u_out is the final rounding when C is 16-bit.  Returns the observed
-    error in units of sqrt(2K) * 2^-24 * S, which stays O(1) for a healthy accumulator."""
+    accumulation of 2K terms in tensor-core order, whose rounding errors add like a random walk
+    (sqrt(2K)); u_out is the final rounding when C is 16-bit (2^-24 for float32, covering the
+    read-out of the accumulator).  A kernel that lost a few accumulator bits, or dropped one of
+    the four real products, fails this gate.  The term-by-term worst case 2 * (2K + 2) * 2^-24 * S
+    is checked as well but can never bind.  Returns the observed error in units of
+    sqrt(2K) * 2^-24 * S."""
     got64 = ou.to_double(got, type_out)
     worst = 0.0
+    u_out = max(out_rounding_unit(type_out), U24)
     for i in range(got64.shape[0]):
         c64, s = ou.double_gemm(type_in, a[i], b[i])
         err = np.abs(got64[i] - c64)
-        tol = 2.0 * (2 * K + 2) * U24 * s + out_rounding_unit(type_out) * np.abs(c64) + 1e-30
+        tol = FP64_GATE_UNITS * math.sqrt(2 * K) * U24 * s + 2.0 * u_out * np.abs(c64) + 1e-30
         bad = err > tol
         assert not bad.any(), "fp64 gate: %d elements off, worst err %g (tol %g)" % (
             int(bad.sum()), float(err[bad].max()), float(tol[bad].max()))
+        assert not (err > 2.0 * (2 * K + 2) * U24 * s + 2.0 * u_out * np.abs(c64) + 1e-30).any()
         if type_out == ou.F32:
             worst = max(worst, float((err / (math.sqrt(2 * K) * U24 * s + 1e-30)).max()))
     return worst

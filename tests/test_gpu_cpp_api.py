@@ -21,4 +21,4 @@ def test_cpp_api_program():
     print(res.stderr, file=sys.stderr)
     assert res.returncode == 0, res.stdout + res.stderr
     assert "0 failure(s)" in res.stdout
-    assert res.stdout.count("PASS") >= 9
+    assert res.stdout.count("PASS") >= 12

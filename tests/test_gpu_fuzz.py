@@ -80,5 +80,7 @@ FLOATS = [(ou.F16, ou.F32), (ou.BF16, ou.F32), (ou.F32, ou.F32), (ou.E4M3, ou.F3
                          ids=lambda c: "%s-%d-B%d-%dx%dx%d" % (ou.TYPE_NAMES[c[1]], c[0], c[3],
                                                                 c[4], c[5], c[6]))
 def test_float_random_shapes_reference_rule(case):
-    got, want, _, _ = _run(case)
+    got, want, a, b = _run(case)
     gu.assert_close_reference_rule(got, want, case[1], case[2])
+    if not case[-1]:  # alpha = 1, beta = 0: the library's own, much tighter, gate applies as well
+        gu.assert_close_fp64(got, case[1], case[2], a, b, case[6])

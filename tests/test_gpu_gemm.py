@@ -305,6 +305,76 @@ def test_int1_config3_k65536_bit_exact():
     assert np.array_equal(got, want)
 
 
+def _step_rows(points, K):
+    """Packed 1-bit rows whose sample k is +1 (bit set) for k < points[r] and -1 after."""
+    kw = K // 32
+    word = np.arange(kw, dtype=np.int64)[None, :]
+    p = np.asarray(points, dtype=np.int64)[:, None]
+    full = word < p // 32
+    part = word == p // 32
+    partial = ((np.uint64(1) << (p % 32).astype(np.uint64)) - np.uint64(1)).astype(np.uint32)
+    return np.where(full, np.uint32(0xFFFFFFFF), np.where(part, partial, np.uint32(0)))
+
+
+def _step_dot(p, q, K):
+    """sum_k a(k) b(k) for two such rows: they agree except between the two steps."""
+    return K - 2 * np.abs(np.asarray(p, np.int64)[:, None] - np.asarray(q, np.int64)[None, :])
+
+
+CORRELATED = [
+    ("k65536-single", 128, 128, 65536, {}),
+    ("k65536-pair", 256, 224, 65536, {}),
+    ("k65536-3planes", 256, 192, 65536, dict(CCGLIB_B200_MXF4_NEGATE="0")),
+    ("k2^22-pair", 256, 128, 1 << 22, {}),
+    ("k2^22-single", 128, 128, 1 << 22, dict(CCGLIB_B200_PAIR="0")),
+    ("k2^22+1024-i8", 128, 128, (1 << 22) + 1024, {}),
+]
+
+
+@pytest.mark.parametrize("case", CORRELATED, ids=[c[0] for c in CORRELATED])
+def test_int1_correlated_inputs_large_sums_bit_exact(case, monkeypatch):
+    """Correlated 1-bit input (what a correlator's autocorrelations look like) drives the sums to
+    +-2K, where random signs only reach sqrt(2K): all-ones rows, rows that are +1 up to a step
+    and -1 after it, and their negations.  The default tensor route accumulates in float32, so
+    every partial sum up to 2K = 2^23 must be held exactly; the answer is known in closed form
+    (rows with steps at p and q agree in K - |p - q| samples)."""
+    _, M, N, K, env = case
+    for key, value in env.items():
+        monkeypatch.setenv(key, value)
+    rng = np.random.default_rng(41)
+
+    def points(rows):
+        p = rng.integers(0, K + 1, rows)
+        p[:4] = [K, K, 0, K // 2]  # all +1, all +1, all -1, half and half
+        return p
+
+    pa_re, pa_im, pb_re, pb_im = points(M), points(M), points(N), points(N)
+    pa_im[0], pb_re[0], pb_im[0] = 0, K, K  # row 0 x column 0: Re = K - (-K) = 2K, Im = 0
+    pa_im[1], pb_re[1], pb_im[1] = K, K, K  # row 1 x column 1: Re = 0, Im = 2K
+    a = np.stack([_step_rows(pa_re, K), _step_rows(pa_im, K)])[None]
+    b = np.stack([_step_rows(pb_re, K), _step_rows(pb_im, K)])[None]
+    want_re = _step_dot(pa_re, pb_re, K) - _step_dot(pa_im, pb_im, K)
+    want_im = _step_dot(pa_re, pb_im, K) + _step_dot(pa_im, pb_re, K)
+    assert want_re[0, 0] == 2 * K and want_im[1, 1] == 2 * K
+    got = gu.run_gemm(ou.INT1, ou.INT32, a, b, 1, M, N, K, variant=capi.BASIC).reshape(2, M, N)
+    assert np.array_equal(got[0], want_re)
+    assert np.array_equal(got[1], want_im)
+
+
+def test_int1_correlated_closed_form_agrees_with_oracle():
+    # the closed form used above, checked against the CPU oracle at a size it finishes quickly
+    M, N, K = 40, 24, 2048
+    rng = np.random.default_rng(42)
+    pts = [rng.integers(0, K + 1, r) for r in (M, M, N, N)]
+    a = np.stack([_step_rows(pts[0], K), _step_rows(pts[1], K)])[None]
+    b = np.stack([_step_rows(pts[2], K), _step_rows(pts[3], K)])[None]
+    want = gu.oracle_batch(ou.INT1, ou.INT32, a, b, 1, M, N, K)[0]
+    assert np.array_equal(want[0], _step_dot(pts[0], pts[2], K) - _step_dot(pts[1], pts[3], K))
+    assert np.array_equal(want[1], _step_dot(pts[0], pts[3], K) + _step_dot(pts[1], pts[2], K))
+    got = gu.run_gemm(ou.INT1, ou.INT32, a, b, 1, M, N, K, variant=capi.BASIC).reshape(2, M, N)
+    assert np.array_equal(got, want)
+
+
 def test_tf32_ignores_low_mantissa_bits():
     """float32 input is consumed as tf32: the 13 low mantissa bits are dropped (truncation), which
     is what the reference assumes (kernels/gemm_kernel_float.cu:80-81) and why its tests mask

@@ -120,8 +120,8 @@ def _run_both(name, seed=5, time_it=False):
                          "variant": info["variant"]}
         print("%s: reference kernel %.3f ms (%.1f TOPS), this library %.3f ms (%.1f TOPS)" % (
             name, ms_ref, ops / ms_ref / 1e9, ms_ours, ops / ms_ours / 1e9))
-        out_dir = os.environ.get("CCGLIB_B200_TIMINGS_DIR", os.path.join(ROOT, "gpurun_out"))
-        if os.path.isdir(out_dir):
+        out_dir = os.environ.get("CCGLIB_B200_TIMINGS_DIR", "")  # unset: nothing is written
+        if out_dir and os.path.isdir(out_dir):
             with open(os.path.join(out_dir, "reference_gpu_timings.json"), "w") as f:
                 json.dump(TIMINGS, f, indent=1)
     plan.close()
