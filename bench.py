@@ -2,16 +2,22 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-One "step" is one pass of the hot path over the whole (per-rank share of the) workload.  The
-default workload is the optimized fp16 -> fp32 complex GEMM on interleaved input, batch 64,
-M = N = K = 8192: Transpose(A), Transpose(B), GEMM, all enqueued on one stream through the C ABI.
-Metric: complex TOPS = 8*M*N*K*batch / time (the reference's benchmark/benchmark_gemm.cpp:79-82).
+One "step" is one pass of the hot path over the whole (per-rank share of the) workload through
+the library's Pipeline object (ccglib_b200_pipeline_run): for the headline workload, the optimized
+fp16 -> fp32 complex GEMM on interleaved input, batch 64, M = N = K = 8192, that is Transpose(A),
+Transpose(B), GEMM on one stream.  Metric: complex TOPS = 8*M*N*K*batch / time (the reference's
+benchmark/benchmark_gemm.cpp:79-82).
 
 * `value`    inputs resident in HBM, CUDA-event time of K steps, max over ranks.
-* `e2e`      the same pass with HOST buffers: pinned host -> device copies of A and B and the
-             device -> host copy of C inside the timed region (double-buffered batch slices).
-* `roofline` the GEMM kernel alone: 8*M*N*K*batch flops per launch / its CUDA-event duration,
-             against the measured tensor peak in MEASURED_PEAKS.json.
+* `e2e`      the same pass with HOST buffers through ccglib_b200_pipeline_run_host: the whole A, B
+             and C live in pinned host memory, the library copies batch slices in, runs them and
+             copies C back, double-buffered; wall clock around K blocking calls.
+* `roofline` the GEMM stage alone: 8*M*N*K*batch flops per launch / its CUDA-event duration,
+             against the measured tensor peak in MEASURED_PEAKS.json (and the HBM roof).
+* `per_workload` the other configurations of the baseline, each device-timed for about two
+             seconds with its own roofline, parity and clock record, and `reference_gpu`: the
+             reference's own legacy kernel (compiled unmodified for sm_100a) timed on the same
+             device and inputs for one batch slice, as a reported baseline and second checker.
 * `cpu_baseline` / `--impl reference`: the reference's own CPU GEMM (oracle/_ref, else the C
              restatement in oracle/) on a bounded sample with all host threads.
 
@@ -42,9 +48,9 @@ NOMINAL_TFLOPS = {"f16": 2250.0, "bf16": 2250.0, "tf32": 1125.0, "e4m3": 4500.0,
 WORKLOADS = {
     "c1_f16_basic_1024": ("f16", "F16", "F32", 1, 1024, 1024, 1024, "basic", "planar"),
     "c2_f16_opt_8192_b64": ("f16", "F16", "F32", 64, 8192, 8192, 8192, "opt", "interleaved"),
-    # 1-bit: Packing, then the GEMM on the packed [batch][2][rows][K/32] words; the GEMM re-stages
-    # 1-bit operands itself, so the Pipeline does not tile them first
-    "c3_int1_4096_k65536_b32": ("int1", "INT1", "INT32", 32, 4096, 4096, 65536, "basic", "bytes"),
+    # 1-bit: one byte per sample, as the reference's Pipeline takes it; the library turns the
+    # bytes into tensor-core operands itself (no Packing or Transpose pass)
+    "c3_int1_4096_k65536_b32": ("int1", "INT1", "INT32", 32, 4096, 4096, 65536, "opt", "bytes"),
     "c4_e4m3_4096_k16384_b32": ("e4m3", "E4M3", "F32", 32, 4096, 4096, 16384, "opt", "planar"),
     "c4_e5m2_4096_k16384_b32": ("e5m2", "E5M2", "F32", 32, 4096, 4096, 16384, "opt", "planar"),
     "c5_bf16_256x2048x512_b4096": ("bf16", "BF16", "F32", 4096, 256, 2048, 512, "basic", "planar"),
@@ -52,14 +58,26 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "c2_f16_opt_8192_b64"
 
+# the reference's own GPU kernel compiled for one batch slice of each workload
+# (oracle/build_reference_gpu.py: CASES)
+REFERENCE_GPU_CASE = {
+    "c1_f16_basic_1024": "c1_f16_basic", "c2_f16_opt_8192_b64": "c2_f16_opt_b2",
+    "c3_int1_4096_k65536_b32": "c3_int1_opt_b1", "c4_e4m3_4096_k16384_b32": "c4_e4m3_opt_b2",
+    "c4_e5m2_4096_k16384_b32": "c4_e5m2_opt_b2",
+    "c5_bf16_256x2048x512_b4096": "c5_bf16_basic_b64",
+    "c5_tf32_256x2048x512_b4096": "c5_tf32_basic_b64",
+}
+
 # value-type codes of the C ABI (= the reference's ValueType ordinals) and their widths in bits
 TYPE_CODE = {"INT1": 0, "INT32": 1, "BF16": 2, "E4M3": 3, "E5M2": 4, "F16": 5, "F32": 6}
 TYPE_BITS = {0: 1, 1: 32, 2: 16, 3: 8, 4: 8, 5: 16, 6: 32}
 
-# DRAM bytes (read + write) of one GEMM launch per batch item, from the ncu capture summarised in
-# profiles/cgemm_tcgen05_f16_opt_8192_batch2_ncu_full.md (6.79 GB for 2 items; items are walked
-# one after another, so traffic grows in proportion to the batch).
+# DRAM bytes (read + write) of one GEMM-kernel launch per batch item, from single-launch ncu
+# captures of small cases (dram__bytes_read.sum + dram__bytes_write.sum; batch items are walked
+# one after another, so the traffic grows in proportion to the batch).  Workloads without a
+# capture report null.
 NCU_DRAM_BYTES_PER_ITEM = {"c2_f16_opt_8192_b64": 3.39e9}
+C1_ROTATE = 16  # config 1 (16 MiB per problem) rotates over 16 operand sets: 256 MiB > L2
 
 
 def measured_peaks() -> dict:
@@ -134,17 +152,33 @@ class ClockSampler:
 
 # --------------------------------------------------------------------------- CPU baseline
 
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_baseline(type_in_name: str, type_out_name: str, K: int, target_s: float = 12.0) -> dict:
     """Times the reference's own CPU GEMM (or the C restatement) on a bounded sample: one batch
-    item of the workload's dtype and K with M = N chosen so the run takes about target_s."""
+    item of the workload's dtype and K with M = N chosen so the run takes about target_s.  The
+    OpenMP thread count is set explicitly (launchers such as torchrun export OMP_NUM_THREADS=1)
+    and the count the runtime reports back is what `cores` states."""
     import oracle_util as ou
 
     type_in = getattr(ou, type_in_name)
     type_out = getattr(ou, type_out_name)
+    want = host_threads()
+    os.environ["OMP_NUM_THREADS"] = str(want)  # before the OpenMP runtime of the oracle loads
     ref = ou.load_reference()
     kind = "reference" if ref is not None else "port"
-    cores = os.cpu_count() or 1
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    if ref is not None:
+        ref.ref_omp_set_threads(want)
+        cores = int(ref.ref_omp_max_threads())
+    else:
+        port = ou.load_port()
+        port.oracle_omp_set_threads(want)
+        cores = int(port.oracle_omp_max_threads())
     rng = np.random.default_rng(7)
 
     def run(M, N, Kk):
@@ -169,15 +203,21 @@ def cpu_baseline(type_in_name: str, type_out_name: str, K: int, target_s: float 
     t = run(mn, mn, K)
     ops = 8.0 * mn * mn * K
     return {"value": ops / t / 1e12, "unit": "TOPS", "cores": cores, "kind": kind,
-            "sample": "1 batch item, M=N=%d, K=%d, %s->%s, %.1f s" % (
-                mn, K, type_in_name.lower(), type_out_name.lower(), t),
+            "sample": "1 batch item, M=N=%d, K=%d, %s->%s, %.1f s, %d OpenMP threads" % (
+                mn, K, type_in_name.lower(), type_out_name.lower(), t, cores),
             "seconds": t}
 
 
 # --------------------------------------------------------------------------- device workload
 
+def _torch_dtype(torch, dtype):
+    return {"f16": torch.float16, "bf16": torch.bfloat16, "tf32": torch.float32,
+            "e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}[dtype]
+
+
 class Workload:
-    """Device-resident buffers and the enqueue function of one pass of the hot path."""
+    """Device-resident operands of one workload and its Pipeline (the library object whose
+    run() is one step)."""
 
     def __init__(self, name: str, batch: int, device):
         import torch
@@ -192,14 +232,16 @@ class Workload:
         self.layout = layout
         self.device = device
         self.bits = TYPE_BITS[self.type_in]
-        self.flops = 8.0 * M * N * K * batch
-        self.launches_per_step = 1
-        self.m_blk, self.n_blk, self.k_c = capi.gemm_dims(self.type_in, self.type_out, self.variant)
+        # config 1 is one 16 MiB problem: rotate over several operand sets so that no step finds
+        # its inputs in L2 (the other workloads are far larger than L2 as they are)
+        self.sets = C1_ROTATE if batch == 1 and 2 * (M + N) * K * self.bits // 8 < (64 << 20) else 1
+        self.step_index = 0
         self._alloc()
 
-    # -- allocation and seeded synthetic inputs (generated on the device, item by item)
+    # -- seeded synthetic inputs, generated on the device item by item
     def _gen(self, rows, seed):
-        torch, B, K = self.torch, self.B, self.K
+        torch, K = self.torch, self.K
+        B = self.B * self.sets
         g = torch.Generator(device=self.device)
         g.manual_seed(seed)
         il = self.layout == "interleaved"
@@ -209,8 +251,7 @@ class Workload:
                 out[b] = torch.randint(0, 2, (2, rows, K), dtype=torch.uint8, device=self.device,
                                        generator=g)
             return out
-        tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "tf32": torch.float32,
-               "e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}[self.dtype]
+        tdt = _torch_dtype(torch, self.dtype)
         shape = (B, rows, K, 2) if il else (B, 2, rows, K)
         out = torch.empty(shape, dtype=tdt, device=self.device)
         for b in range(B):
@@ -226,70 +267,49 @@ class Workload:
             del x
         return out
 
-    def _tiled_bytes(self, rows, blk):
-        rt = -(-rows // blk)
-        kt = -(-self.K // self.k_c)
-        return self.B * rt * kt * 2 * blk * self.k_c * self.bits // 8
-
     def _alloc(self):
         torch, capi = self.torch, self.capi
         rank_seed = 0xCC61B + 17 * int(os.environ.get("RANK", "0"))
         self.a_in = self._gen(self.M, rank_seed + 1)
         self.b_in = self._gen(self.N, rank_seed + 2)
-        self.a_gemm, self.b_gemm = self.a_in, self.b_in
-        if self.layout == "bytes":
-            self.a_packed = torch.empty(self.a_in.numel() // 8, dtype=torch.uint8,
-                                        device=self.device)
-            self.b_packed = torch.empty(self.b_in.numel() // 8, dtype=torch.uint8,
-                                        device=self.device)
-            self.a_gemm, self.b_gemm = self.a_packed, self.b_packed
-            self.launches_per_step += 2
-        if self.variant == capi.OPT:
-            self.a_tiled = torch.empty(self._tiled_bytes(self.M, self.m_blk), dtype=torch.uint8,
-                                       device=self.device)
-            self.b_tiled = torch.empty(self._tiled_bytes(self.N, self.n_blk), dtype=torch.uint8,
-                                       device=self.device)
-            self.a_gemm, self.b_gemm = self.a_tiled, self.b_tiled
-            self.launches_per_step += 2
         out_dt = torch.int32 if self.type_out == TYPE_CODE["INT32"] else torch.float32
-        self.c = torch.empty((self.B, 2, self.M, self.N), dtype=out_dt, device=self.device)
-        self.plan = capi.GemmPlan(self.B, self.M, self.N, self.K, self.type_in, self.type_out,
-                                  variant=self.variant)
-        self.launches_per_step += self.plan.launches - 1
+        self.c = torch.empty((self.B * self.sets, 2, self.M, self.N), dtype=out_dt,
+                             device=self.device)
+        in_axis = capi.INTERLEAVED if self.layout == "interleaved" else capi.PLANAR
+        self.pipe = capi.Pipeline(self.B, self.M, self.N, self.K, self.type_in, self.type_out,
+                                  variant=self.variant, input_complex_axis=in_axis)
+        self.launches_per_step = self.pipe.launches
+        self.item_a = self.a_in[0].numel() * self.a_in.element_size()
+        self.item_b = self.b_in[0].numel() * self.b_in.element_size()
+        self.item_c = self.c[0].numel() * 4
 
     def hbm_bytes(self):
         n = sum(t.numel() * t.element_size() for t in (self.a_in, self.b_in, self.c))
-        for name in ("a_packed", "b_packed", "a_tiled", "b_tiled"):
-            if hasattr(self, name):
-                n += getattr(self, name).numel()
-        return n + self.plan.scratch_bytes
+        return n + self.pipe.scratch_bytes
 
-    # -- one pass; returns (event before GEMM, event after GEMM) when asked
-    def step(self, stream_handle: int, gemm_events=None):
-        capi = self.capi
-        a, b = self.a_in, self.b_in
-        in_axis = capi.INTERLEAVED if self.layout == "interleaved" else capi.PLANAR
+    def describe_step(self):
         if self.layout == "bytes":
-            capi.pack(a.numel(), capi.FORWARD, capi.PLANAR, a.data_ptr(), self.a_packed.data_ptr(),
-                      stream_handle)
-            capi.pack(b.numel(), capi.FORWARD, capi.PLANAR, b.data_ptr(), self.b_packed.data_ptr(),
-                      stream_handle)
-            a, b = self.a_packed, self.b_packed
-        if self.variant == capi.OPT:
-            capi.transpose(self.B, self.M, self.K, self.m_blk, self.k_c, self.bits, in_axis,
-                           a.data_ptr(), self.a_tiled.data_ptr(), stream_handle)
-            capi.transpose(self.B, self.N, self.K, self.n_blk, self.k_c, self.bits, in_axis,
-                           b.data_ptr(), self.b_tiled.data_ptr(), stream_handle)
+            return "byte samples -> operand expansion + GEMM, %d launches" % self.launches_per_step
+        if self.variant == self.capi.OPT:
+            return "transpose A, B + GEMM"
+        return "GEMM"
+
+    # -- one pass through the library's Pipeline; gemm_events = (begin, end) torch events
+    def step(self, stream_handle: int, gemm_events=None):
+        s = self.step_index % self.sets
+        self.step_index += 1
         if gemm_events is not None:
-            gemm_events[0].record()
-        self.plan.run(self.a_gemm.data_ptr(), self.b_gemm.data_ptr(), self.c.data_ptr(),
-                      stream_handle)
+            self.pipe.set_gemm_events(gemm_events[0].cuda_event, gemm_events[1].cuda_event)
+        self.pipe.run(self.a_in.data_ptr() + s * self.B * self.item_a,
+                      self.b_in.data_ptr() + s * self.B * self.item_b,
+                      self.c.data_ptr() + s * self.B * self.item_c, stream_handle)
         if gemm_events is not None:
-            gemm_events[1].record()
+            self.pipe.set_gemm_events(None, None)
 
     # -- sampled parity check against float64 dot products of the same stored inputs
-    def spot_check(self, samples=48):
+    def spot_check(self, samples=48, c=None):
         torch = self.torch
+        c = self.c if c is None else c
         g = torch.Generator(device="cpu")
         g.manual_seed(1234)
         worst = 0.0
@@ -315,16 +335,17 @@ class Workload:
             im = float((ar * bi).sum() + (ai * br).sum())
             s_re = float((ar.abs() * br.abs()).sum() + (ai.abs() * bi.abs()).sum())
             s_im = float((ar.abs() * bi.abs()).sum() + (ai.abs() * br.abs()).sum())
-            got_re, got_im = float(self.c[b, 0, m, n]), float(self.c[b, 1, m, n])
+            got_re, got_im = float(c[b, 0, m, n]), float(c[b, 1, m, n])
             if self.type_in == TYPE_CODE["INT1"]:
                 if got_re != re or got_im != im:
                     return {"samples": samples, "ok": False, "worst_err_over_tol": float("inf")}
                 continue
             for got, want, s in ((got_re, re, s_re), (got_im, im, s_im)):
-                tol = 2.0 * (2 * K + 2) * 2.0 ** -24 * s + 1e-30
+                # the library's stated gate: 4 sqrt(2K) 2^-24 S + 2 * 2^-24 |c|
+                tol = 4.0 * math.sqrt(2 * K) * 2.0 ** -24 * s + 2.0 ** -23 * abs(want) + 1e-30
                 worst = max(worst, abs(got - want) / tol)
-        return {"samples": samples, "ok": worst <= 1.0, "worst_err_over_tol": worst}
-
+        return {"samples": samples, "ok": worst <= 1.0, "worst_err_over_tol": worst,
+                "gate": "4*sqrt(2K)*2^-24*S + 2^-23*|c| (exact for 1-bit)"}
 
     def _planes_f64(self, t, b):
         """(re, im) float64 planes [rows][K] of batch item b of an input tensor, as the GEMM sees
@@ -382,116 +403,133 @@ class Workload:
             worst = max(worst, float((err / tol).max()))
         return {"items": items, "ok": worst <= 1.0, "worst_err_over_tol": worst}
 
+    # -- the reference's own GPU kernel on the first batch items of the same inputs
+    def reference_gpu(self, stream_handle: int):
+        """Runs the reference project's legacy WMMA / mma.sync kernel (compiled unmodified for
+        sm_100a, one cubin per workload slice) on the first batch items of this workload's
+        operands, compares its C with this library's for those items and times it.  Reported
+        baseline and second checker only."""
+        torch, capi = self.torch, self.capi
+        try:
+            import reference_gpu as rg
+        except ImportError:
+            return {"unavailable": "tests/reference_gpu.py not importable"}
+        case = REFERENCE_GPU_CASE.get(self.name)
+        if not rg.available() or case not in rg.manifest():
+            return {"unavailable": "the reference's GPU kernels were not compiled "
+                                   "(oracle/build_reference_gpu.py needs the reference checkout)"}
+        info = rg.manifest()[case]
+        nb = min(info["B"], self.B)
+        if nb != info["B"]:
+            return {"unavailable": "this rank holds fewer than %d batch items" % info["B"]}
+        M, N, K = self.M, self.N, self.K
+        a, b = self.a_in[:nb], self.b_in[:nb]
+        bits, in_axis = self.bits, capi.PLANAR
+        if self.layout == "interleaved":
+            in_axis = capi.INTERLEAVED
+        if self.layout == "bytes":  # the reference packs first (src/pipeline/Pipeline.cpp:108-112)
+            pa = torch.empty(a.numel() // 8, dtype=torch.uint8, device=self.device)
+            pb = torch.empty(b.numel() // 8, dtype=torch.uint8, device=self.device)
+            capi.pack(a.numel(), capi.FORWARD, capi.PLANAR, a.data_ptr(), pa.data_ptr(),
+                      stream_handle)
+            capi.pack(b.numel(), capi.FORWARD, capi.PLANAR, b.data_ptr(), pb.data_ptr(),
+                      stream_handle)
+            a, b = pa, pb
+        if info["variant"] == "opt":  # the reference kernel's own tile contract
+            def tiled(x, rows, blk):
+                rt, kt = -(-rows // blk), -(-K // info["k_chunk"])
+                out = torch.zeros(nb * rt * kt * 2 * blk * info["k_chunk"] * bits // 8,
+                                  dtype=torch.uint8, device=self.device)
+                capi.transpose(nb, rows, K, blk, info["k_chunk"], bits, in_axis, x.data_ptr(),
+                               out.data_ptr(), stream_handle)
+                return out
+            a, b = tiled(a, M, info["m_blk"]), tiled(b, N, info["n_blk"])
+        elif in_axis != capi.PLANAR:
+            return {"unavailable": "the reference's basic kernel reads planar input only"}
+        c_ref = torch.zeros((nb, 2, M, N), dtype=self.c.dtype, device=self.device)
+
+        def launch():
+            rg.launch(case, c_ref.data_ptr(), a.data_ptr(), b.data_ptr(), stream_handle)
+
+        launch()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            launch()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        ms = float(np.mean(times))
+        ours = self.c[:nb]
+        if self.type_in == TYPE_CODE["INT1"]:
+            agrees = bool(torch.equal(ours, c_ref))
+            rule = "identical"
+        else:
+            eps = {"f16": 2.0 ** -10, "bf16": 2.0 ** -7, "tf32": 2.0 ** -10, "e4m3": 0.125,
+                   "e5m2": 0.25}[self.dtype]
+            rel = (ours - c_ref).abs() / (ours.abs() + c_ref.abs() + 1.0)
+            agrees = bool(float(rel.max()) <= 10.0 * eps)
+            rule = "|x-y|/(|x|+|y|+1) <= 10 eps(Tin), the reference's test/gemm/fpequals.h rule"
+        ops = 8.0 * M * N * K * nb
+        return {"kernel": info["entry"] + " (reference kernels/, sm_100a cubin)", "batch": nb,
+                "ms": ms, "tops": ops / ms / 1e9, "agrees_with_this_library": agrees,
+                "rule": rule}
+
 
 # --------------------------------------------------------------------------- end-to-end pass
 
-class HostPipeline:
-    """The same pass with HOST buffers: slices of the batch are copied from pinned host memory,
-    transposed, multiplied and copied back, double-buffered over three streams so copies overlap
-    compute.  Only built for workloads whose step is transpose + GEMM or GEMM alone."""
+class HostRun:
+    """The same pass with HOST operands through the library's own host-memory call
+    (ccglib_b200_pipeline_run_host, the counterpart of the reference's Pipeline::Run(HostMemory)):
+    whole A, B and C in pinned host memory, filled from the seeded device inputs."""
 
-    def __init__(self, name: str, batch: int, device, slice_items: int):
-        import torch
+    def __init__(self, wl: Workload):
+        torch = wl.torch
+        self.wl = wl
+        t0 = time.perf_counter()
+        nbytes = lambda t: wl.B * t[0].numel() * t.element_size()
+        self.h_a = torch.empty(nbytes(wl.a_in), dtype=torch.uint8, pin_memory=True)
+        self.h_b = torch.empty(nbytes(wl.b_in), dtype=torch.uint8, pin_memory=True)
+        self.h_c = torch.empty(nbytes(wl.c), dtype=torch.uint8, pin_memory=True)
+        self.h_a.copy_(wl.a_in[:wl.B].reshape(-1).view(torch.uint8))
+        self.h_b.copy_(wl.b_in[:wl.B].reshape(-1).view(torch.uint8))
+        self.h_c.zero_()
+        torch.cuda.synchronize()
+        self.setup_s = time.perf_counter() - t0
+        self.h2d_bytes = self.h_a.numel() + self.h_b.numel()
+        self.d2h_bytes = self.h_c.numel()
 
-        from ccglib_b200 import capi
+    def step(self, stream_handle):
+        self.wl.pipe.run_host(self.h_a.data_ptr(), self.h_b.data_ptr(), self.h_c.data_ptr(),
+                              stream_handle)
 
-        self.torch, self.capi = torch, capi
-        dtype, tin, tout, _, M, N, K, variant, layout = WORKLOADS[name]
-        self.B, self.M, self.N, self.K = batch, M, N, K
-        self.type_in, self.type_out = TYPE_CODE[tin], TYPE_CODE[tout]
-        self.bits = TYPE_BITS[self.type_in]
-        if slice_items <= 0:  # about 1 GiB of input per slice
-            per_item = 2 * (M + N) * K * (8 if layout == "bytes" else self.bits) // 8
-            slice_items = max(1, (1 << 30) // per_item)
-        self.S = max(1, min(slice_items, batch))
-        while batch % self.S:
-            self.S -= 1
-        self.variant = capi.OPT if variant == "opt" else capi.BASIC
-        self.layout = layout
-        self.packed = layout == "bytes"
-        S = self.S
-        in_bytes_a = S * 2 * M * K * (8 if self.packed else self.bits) // 8
-        in_bytes_b = S * 2 * N * K * (8 if self.packed else self.bits) // 8
-        c_bytes = S * 2 * M * N * 4
-        self.h2d_bytes = (in_bytes_a + in_bytes_b) * (batch // S)
-        self.d2h_bytes = c_bytes * (batch // S)
-        u8 = torch.uint8
-        g = torch.Generator()
-        g.manual_seed(99)
-        # host slices hold valid patterns of the input type (small fp16-like magnitudes / 0-1)
-        self.h_a = torch.empty(in_bytes_a, dtype=u8).pin_memory()
-        self.h_b = torch.empty(in_bytes_b, dtype=u8).pin_memory()
-        self.h_c = torch.empty(c_bytes, dtype=u8).pin_memory()
-        if self.packed:
-            self.h_a.copy_(torch.randint(0, 2, (in_bytes_a,), dtype=u8, generator=g))
-            self.h_b.copy_(torch.randint(0, 2, (in_bytes_b,), dtype=u8, generator=g))
-        else:
-            # byte 0x2c in every position decodes to a small finite value in f16/bf16/fp8/f32
-            self.h_a.fill_(0x2C)
-            self.h_b.fill_(0x2C)
-        self.d_a = [torch.empty(in_bytes_a, dtype=u8, device=device) for _ in range(2)]
-        self.d_b = [torch.empty(in_bytes_b, dtype=u8, device=device) for _ in range(2)]
-        self.d_c = [torch.empty(c_bytes, dtype=u8, device=device) for _ in range(2)]
-        self.m_blk, self.n_blk, self.k_c = capi.gemm_dims(self.type_in, self.type_out, self.variant)
-        if self.packed:
-            self.p_a = torch.empty(in_bytes_a // 8, dtype=u8, device=device)
-            self.p_b = torch.empty(in_bytes_b // 8, dtype=u8, device=device)
-        if self.variant == capi.OPT:
-            tb = lambda rows, blk: (S * (-(-rows // blk)) * (-(-K // self.k_c)) * 2 * blk *
-                                    self.k_c * self.bits // 8)
-            self.t_a = torch.empty(tb(M, self.m_blk), dtype=u8, device=device)
-            self.t_b = torch.empty(tb(N, self.n_blk), dtype=u8, device=device)
-        self.plan = capi.GemmPlan(S, M, N, K, self.type_in, self.type_out, variant=self.variant)
-        self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(device=device) for _ in range(3))
-        self.ev_in = [torch.cuda.Event() for _ in range(2)]
-        self.ev_cmp = [torch.cuda.Event() for _ in range(2)]
-        self.ev_out = [torch.cuda.Event() for _ in range(2)]
-
-    def step(self):
-        torch, capi = self.torch, self.capi
-        S, M, N, K = self.S, self.M, self.N, self.K
-        in_axis = capi.INTERLEAVED if self.layout == "interleaved" else capi.PLANAR
-        for i in range(self.B // S):
-            buf = i & 1
-            with torch.cuda.stream(self.s_in):
-                self.s_in.wait_event(self.ev_cmp[buf])
-                self.d_a[buf].copy_(self.h_a, non_blocking=True)
-                self.d_b[buf].copy_(self.h_b, non_blocking=True)
-                self.ev_in[buf].record()
-            with torch.cuda.stream(self.s_cmp):
-                self.s_cmp.wait_event(self.ev_in[buf])
-                self.s_cmp.wait_event(self.ev_out[buf])
-                h = int(self.s_cmp.cuda_stream)
-                a, b = self.d_a[buf], self.d_b[buf]
-                if self.packed:
-                    capi.pack(a.numel(), capi.FORWARD, capi.PLANAR, a.data_ptr(),
-                              self.p_a.data_ptr(), h)
-                    capi.pack(b.numel(), capi.FORWARD, capi.PLANAR, b.data_ptr(),
-                              self.p_b.data_ptr(), h)
-                    a, b = self.p_a, self.p_b
-                if self.variant == capi.OPT:
-                    capi.transpose(S, M, K, self.m_blk, self.k_c, self.bits, in_axis, a.data_ptr(),
-                                   self.t_a.data_ptr(), h)
-                    capi.transpose(S, N, K, self.n_blk, self.k_c, self.bits, in_axis, b.data_ptr(),
-                                   self.t_b.data_ptr(), h)
-                    a, b = self.t_a, self.t_b
-                self.plan.run(a.data_ptr(), b.data_ptr(), self.d_c[buf].data_ptr(), h)
-                self.ev_cmp[buf].record()
-            with torch.cuda.stream(self.s_out):
-                self.s_out.wait_event(self.ev_cmp[buf])
-                self.h_c.copy_(self.d_c[buf], non_blocking=True)
-                self.ev_out[buf].record()
-
-    def time_steps(self, steps, warmup):
-        torch = self.torch
+    def time_steps(self, steps, warmup, stream_handle):
+        torch = self.wl.torch
         for _ in range(warmup):
-            self.step()
+            self.step(stream_handle)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         for _ in range(steps):
-            self.step()
+            self.step(stream_handle)  # blocks until C is complete in host memory
         torch.cuda.synchronize()
         return (time.perf_counter() - t0) / steps
+
+    def check(self):
+        """The C that came back to host memory against the device-resident C of the device-timed
+        steps (same kernels, same inputs: identical), first and last batch item in full, and
+        against float64 dot products on sampled elements."""
+        torch, wl = self.wl.torch, self.wl
+        item = wl.item_c
+        same = True
+        for b in sorted({0, wl.B - 1}):
+            back = self.h_c[b * item:(b + 1) * item].to(wl.device)
+            same = same and bool(torch.equal(back, wl.c[b].reshape(-1).view(torch.uint8)))
+        h_view = self.h_c.view(wl.c.dtype).reshape(wl.B, 2, wl.M, wl.N)
+        spot = wl.spot_check(samples=16, c=h_view)
+        return {"host_c_equals_device_c": same, "sampled_fp64": spot["ok"],
+                "ok": bool(same and spot["ok"])}
 
 
 # --------------------------------------------------------------------------- main arms
@@ -525,13 +563,105 @@ def run_reference_arm(args, name):
     print(json.dumps(line), flush=True)
 
 
+def roofline_of(name, dtype, M, N, K, bits, items, gemm_ms, peaks):
+    scale = NOMINAL_TFLOPS[dtype] / NOMINAL_TFLOPS["bf16"]
+    peak = peaks["bf16_tflops_sustained"] * scale
+    achieved = 8.0 * M * N * K * items / (gemm_ms * 1e-3) / 1e12
+    r = {
+        "bound": "tensor", "kernel": "cgemm_pair_kernel" if dtype == "int1" else
+        "cgemm_tcgen05_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+        "frac": achieved / peak,
+        "traffic": (NCU_DRAM_BYTES_PER_ITEM[name] * items
+                    if name in NCU_DRAM_BYTES_PER_ITEM else None),
+        "traffic_source": ("single-launch ncu capture of a 2-item case, scaled by the batch"
+                           if name in NCU_DRAM_BYTES_PER_ITEM else
+                           "no ncu capture of this workload's kernel is wired in"),
+        "algorithmic_bytes": items * (2.0 * (M + N) * K * bits / 8 + 2.0 * M * N * 4),
+        "peak_source": "%s sustained bf16 GEMM x %.2g (nominal dtype rate ratio%s)" % (
+            peaks["source"], scale,
+            "; a proxy: the 4-bit pipe is not in MEASURED_PEAKS, quote frac_of_nominal"
+            if dtype == "int1" else ""),
+        "frac_of_burst": achieved / (peaks["bf16_tflops"] * scale),
+        "frac_of_nominal": achieved / NOMINAL_TFLOPS[dtype],
+        "gemm_ms_per_launch": gemm_ms,
+    }
+    # the other roof, for shapes near the ridge (config 5): algorithmic bytes / time
+    r["hbm_gbs_achieved"] = r["algorithmic_bytes"] / (gemm_ms * 1e-3) / 1e9
+    r["hbm_frac"] = r["hbm_gbs_achieved"] / peaks["hbm_gbs"]
+    if r["hbm_frac"] > r["frac"]:
+        r.update(bound="hbm", achieved=r["hbm_gbs_achieved"], peak=peaks["hbm_gbs"], unit="GB/s",
+                 frac=r["hbm_frac"], tensor_tflops_achieved=achieved, tensor_frac=achieved / peak)
+    return r
+
+
+def measure_device(wl, steps, warmup, sampler, dist, world):
+    """Warm-up, then `steps` timed steps between CUDA events on the launch stream, each GEMM
+    stage with its own event pair; returns (ms per step, GEMM ms per launch, clocks), the
+    times as max over ranks."""
+    torch, capi = wl.torch, wl.capi
+    stream = torch.cuda.current_stream()
+    handle = int(stream.cuda_stream)
+    for _ in range(max(warmup, 3)):
+        wl.step(handle)
+    torch.cuda.synchronize()
+    status = capi.device_status()
+    if status:
+        raise SystemExit("device status word 0x%x after warm-up" % status)
+    gemm_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+               for _ in range(min(steps, 200))]
+    for a, b in gemm_ev:  # torch creates the CUDA event at its first record: the handles must exist
+        a.record()
+        b.record()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    if sampler is not None:
+        sampler.start()
+        time.sleep(0.25)
+    start.record()
+    for i in range(steps):
+        wl.step(handle, gemm_ev[i] if i < len(gemm_ev) else None)
+    stop.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop() if sampler is not None else None
+    ms_total = start.elapsed_time(stop)
+    gemm_ms = float(np.mean([a.elapsed_time(b) for a, b in gemm_ev]))
+    status = capi.device_status()
+    if status:
+        raise SystemExit("device status word 0x%x in the timed region" % status)
+    t = torch.tensor([ms_total, gemm_ms], dtype=torch.float64, device=wl.device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0]) / steps, float(t[1]), clocks
+
+
+def steps_for(wl, seconds, dist, world):
+    """Steps that fill about `seconds` of device time (same count on every rank)."""
+    torch = wl.torch
+    handle = int(torch.cuda.current_stream().cuda_stream)
+    for _ in range(3):
+        wl.step(handle)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        wl.step(handle)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / 3.0], dtype=torch.float64, device=wl.device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return int(max(5, min(100000, math.ceil(seconds * 1e3 / max(float(t[0]), 1e-3)))))
+
+
 def run_ours(args, name):
     import torch
     import torch.distributed as dist
 
-    from ccglib_b200 import capi
+    from ccglib_b200 import capi, sharding
 
-    dtype, tin, tout, B_total, M, N, K, variant, layout = WORKLOADS[name]
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -543,122 +673,117 @@ def run_ours(args, name):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
+    peaks = measured_peaks()
+    handle = int(torch.cuda.current_stream().cuda_stream)
+
+    def config_of(wname, B_total, share, wl, hbm_gb):
+        dtype, tin, tout, _, M, N, K, variant, layout = WORKLOADS[wname]
+        return {"workload": wname, "batch": B_total, "batch_per_gpu": share, "M": M, "N": N,
+                "K": K, "variant": variant, "input": layout, "step": wl.describe_step(),
+                "l2": ("operands rotate over %d sets (%.0f MB) larger than L2" % (
+                    wl.sets, hbm_gb * 1e3) if wl.sets > 1 else
+                    "inputs larger than L2 (%.1f GB resident per GPU)" % hbm_gb),
+                "parallelism": "batch split over %d GPU(s), no collective" % world}
+
+    # ---- headline workload
+    dtype, tin, tout, B_total, M, N, K, variant, layout = WORKLOADS[name]
     if args.batch:
         B_total = args.batch
     # batch items are independent GEMMs: rank r takes a contiguous share, no collective needed
-    from ccglib_b200 import sharding
-
     share = sharding.batch_shares(B_total, world)
     B = share[rank]
     if B == 0:
         raise SystemExit("batch %d cannot be split over %d ranks" % (B_total, world))
-
     wl = Workload(name, B, device)
-    stream = torch.cuda.current_stream()
-    handle = int(stream.cuda_stream)
-    for _ in range(max(args.warmup, 3)):
-        wl.step(handle)
-    torch.cuda.synchronize()
-    status = capi.device_status()
-    if status:
-        raise SystemExit("device status word 0x%x after warm-up" % status)
-
-    sampler = ClockSampler(local_rank)
-    gemm_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-               for _ in range(args.steps)]
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.25)
-    start.record()
-    for i in range(args.steps):
-        wl.step(handle, gemm_ev[i])
-    stop.record()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    ms_total = start.elapsed_time(stop)
-    gemm_ms = float(np.mean([a.elapsed_time(b) for a, b in gemm_ev]))
-    status = capi.device_status()
-    if status:
-        raise SystemExit("device status word 0x%x in the timed region" % status)
-    t = torch.tensor([ms_total, gemm_ms], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t[0]) / args.steps
-    gemm_ms_max = float(t[1])
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms_step, gemm_ms, clocks = measure_device(wl, args.steps, args.warmup, sampler, dist, world)
     check = wl.spot_check()
     check["freivalds"] = wl.freivalds()
     check["ok"] = bool(check["ok"] and check["freivalds"]["ok"])
-    wl_bits = wl.bits
+    ref_gpu = wl.reference_gpu(handle) if rank == 0 and not args.no_reference_gpu else None
     hbm_gb = wl.hbm_bytes() / 1e9
     launches = wl.launches_per_step * args.steps
     total_flops = 8.0 * M * N * K * B_total
     value = total_flops / (ms_step * 1e-3) / 1e12
+    roofline = roofline_of(name, dtype, M, N, K, wl.bits, share[0], gemm_ms, peaks)
+    config = config_of(name, B_total, share[0], wl, hbm_gb)
 
-    # ---- end to end with host buffers (all ranks run it, rank 0 reports the max time)
+    # ---- end to end with host operands (every rank runs it; the slowest rank's time counts)
     e2e = None
     if not args.no_e2e:
-        del wl
-        torch.cuda.empty_cache()
-        hp = HostPipeline(name, B, device, args.e2e_slice)
+        hr = HostRun(wl)
         if world > 1:
             dist.barrier()
-        sec = hp.time_steps(max(1, args.e2e_steps), 1)
+        sec = hr.time_steps(max(1, args.e2e_steps), 1, handle)
         te = torch.tensor([sec], dtype=torch.float64, device=device)
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
         e2e = {"value": total_flops / float(te[0]) / 1e12, "unit": "TOPS",
-               "h2d_bytes_per_step": hp.h2d_bytes * world, "d2h_bytes_per_step": hp.d2h_bytes * world,
-               "ms_per_step": float(te[0]) * 1e3, "slice_items": hp.S}
+               "h2d_bytes_per_step": hr.h2d_bytes * world, "d2h_bytes_per_step": hr.d2h_bytes * world,
+               "ms_per_step": float(te[0]) * 1e3, "steps": max(1, args.e2e_steps), "warmup": 1,
+               "slice_items": wl.pipe.host_slice,
+               "call": "ccglib_b200_pipeline_run_host (ccglib::pipeline::Pipeline::Run on host "
+                       "memory): whole A, B, C pinned on the host, sliced and double-buffered "
+                       "inside the library",
+               "host_setup_s": hr.setup_s, "check": hr.check()}
         status = capi.device_status()
         if status:
             raise SystemExit("device status word 0x%x in the end-to-end pass" % status)
-        del hp
+        del hr
+    del wl
+    torch.cuda.empty_cache()
+
+    # ---- the other workloads of the baseline, each device-timed for about two seconds
+    per_workload = None
+    if args.per_workload and args.workload is None:
+        per_workload = {}
+        for other in sorted(WORKLOADS):
+            if other == name:
+                continue
+            o_dtype, o_tin, o_tout, o_B, o_M, o_N, o_K, o_variant, o_layout = WORKLOADS[other]
+            if o_B < world:
+                if rank == 0:
+                    per_workload[other] = {"skipped": "batch %d cannot be split over %d GPUs "
+                                                      "(replicas only)" % (o_B, world)}
+                continue
+            o_share = sharding.batch_shares(o_B, world)
+            owl = Workload(other, o_share[rank], device)
+            o_steps = steps_for(owl, args.per_workload_seconds, dist, world)
+            o_sampler = ClockSampler(local_rank) if rank == 0 else None
+            o_ms, o_gemm_ms, o_clocks = measure_device(owl, o_steps, 3, o_sampler, dist, world)
+            o_check = owl.spot_check()
+            o_check["freivalds"] = owl.freivalds()
+            o_check["ok"] = bool(o_check["ok"] and o_check["freivalds"]["ok"])
+            ok_all = torch.tensor([1.0 if o_check["ok"] else 0.0], device=device)
+            if world > 1:
+                dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)
+            o_check["ok_on_every_rank"] = bool(float(ok_all[0]) == 1.0)
+            if rank == 0:
+                o_hbm = owl.hbm_bytes() / 1e9
+                per_workload[other] = {
+                    "value": 8.0 * o_M * o_N * o_K * o_B / (o_ms * 1e-3) / 1e12, "unit": "TOPS",
+                    "dtype": o_dtype, "ms_per_step": o_ms, "steps": o_steps, "warmup": 3,
+                    "config": config_of(other, o_B, o_share[0], owl, o_hbm),
+                    "roofline": roofline_of(other, o_dtype, o_M, o_N, o_K, owl.bits, o_share[0],
+                                            o_gemm_ms, peaks),
+                    "gpu_launches": owl.launches_per_step * o_steps,
+                    "parity": o_check, "clocks": o_clocks,
+                    "reference_gpu": (None if args.no_reference_gpu
+                                      else owl.reference_gpu(handle)),
+                }
+            del owl
+            torch.cuda.empty_cache()
 
     if rank == 0:
-        peaks = measured_peaks()
-        scale = NOMINAL_TFLOPS[dtype] / NOMINAL_TFLOPS["bf16"]
-        peak = peaks["bf16_tflops_sustained"] * scale
-        gemm_flops_rank = 8.0 * M * N * K * share[0]
-        achieved = gemm_flops_rank / (gemm_ms_max * 1e-3) / 1e12
-        roofline = {
-            "bound": "tensor", "kernel": "cgemm_tcgen05_kernel", "achieved": achieved,
-            "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-            "traffic": (NCU_DRAM_BYTES_PER_ITEM[name] * share[0]
-                        if name in NCU_DRAM_BYTES_PER_ITEM else None),
-            "algorithmic_bytes": share[0] * (2.0 * (M + N) * K * wl_bits / 8 + 2.0 * M * N * 4),
-            "peak_source": "%s sustained bf16 GEMM x %.2g (dtype rate ratio)" % (
-                peaks["source"], scale),
-            "frac_of_burst": achieved / (peaks["bf16_tflops"] * scale),
-            "frac_of_nominal": achieved / NOMINAL_TFLOPS[dtype],
-            "gemm_ms_per_launch": gemm_ms_max,
-        }
-        # the other roof, for shapes near the ridge (config 5): algorithmic bytes / time
-        roofline["hbm_gbs_achieved"] = roofline["algorithmic_bytes"] / (gemm_ms_max * 1e-3) / 1e9
-        roofline["hbm_frac"] = roofline["hbm_gbs_achieved"] / peaks["hbm_gbs"]
-        if roofline["hbm_frac"] > roofline["frac"]:
-            roofline.update(bound="hbm", achieved=roofline["hbm_gbs_achieved"],
-                            peak=peaks["hbm_gbs"], unit="GB/s", frac=roofline["hbm_frac"],
-                            tensor_tflops_achieved=achieved, tensor_frac=achieved / peak)
         base = None if args.no_cpu_baseline or world > 1 else cpu_baseline(tin, tout, K)
         line = {
             "metric": "complex_tops", "value": value, "unit": "TOPS", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype,
-            "data": "synthetic",
-            "config": {"workload": name, "batch": B_total, "batch_per_gpu": share[0], "M": M,
-                       "N": N, "K": K, "variant": variant, "input": layout,
-                       "step": ("transpose A, B + GEMM" if variant == "opt" else
-                                "pack A, B + GEMM" if layout == "bytes" else "GEMM"),
-                       "l2": "inputs larger than L2 (%.1f GB resident per GPU)" % hbm_gb,
-                       "parallelism": "batch split over %d GPU(s), no collective" % world},
+            "data": "synthetic", "config": config,
             "roofline": roofline, "cpu_baseline": base, "e2e": e2e, "gpu_launches": launches,
-            "clocks": clocks, "parity": check,
+            "clocks": clocks, "parity": check, "reference_gpu": ref_gpu,
+            "per_workload": per_workload,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -668,21 +793,25 @@ def run_ours(args, name):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                    help="run this workload alone (default: the headline workload plus a "
+                         "per_workload block for all the others)")
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (experiments)")
-    ap.add_argument("--e2e-steps", type=int, default=2)
-    ap.add_argument("--e2e-slice", type=int, default=0,
-                    help="batch items per host slice (0: about 1 GiB of input)")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--per-workload-seconds", type=float, default=2.0)
+    ap.add_argument("--no-per-workload", dest="per_workload", action="store_false")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-gpu", action="store_true")
     args = ap.parse_args()
+    name = args.workload or DEFAULT_WORKLOAD
     if args.impl == "reference":
-        run_reference_arm(args, args.workload)
+        run_reference_arm(args, name)
     else:
-        run_ours(args, args.workload)
+        run_ours(args, name)
 
 
 if __name__ == "__main__":

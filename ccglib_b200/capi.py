@@ -27,6 +27,7 @@ EXPORTS = [
     "ccglib_b200_pipeline_create", "ccglib_b200_pipeline_run", "ccglib_b200_pipeline_run_host",
     "ccglib_b200_pipeline_host_slice", "ccglib_b200_pipeline_set_host_slice",
     "ccglib_b200_pipeline_launches", "ccglib_b200_pipeline_scratch_bytes",
+    "ccglib_b200_pipeline_set_gemm_events",
     "ccglib_b200_pipeline_destroy",
 ]
 
@@ -107,6 +108,8 @@ def lib() -> ctypes.CDLL:
         L.ccglib_b200_pipeline_host_slice.restype = sz
         L.ccglib_b200_pipeline_set_host_slice.argtypes = [vp, sz]
         L.ccglib_b200_pipeline_set_host_slice.restype = ci
+        L.ccglib_b200_pipeline_set_gemm_events.argtypes = [vp, vp, vp]
+        L.ccglib_b200_pipeline_set_gemm_events.restype = ci
         L.ccglib_b200_pipeline_launches.argtypes = [vp]
         L.ccglib_b200_pipeline_launches.restype = sz
         L.ccglib_b200_pipeline_scratch_bytes.argtypes = [vp]
@@ -196,6 +199,10 @@ class Pipeline:
     @host_slice.setter
     def host_slice(self, items: int) -> None:
         _check(lib().ccglib_b200_pipeline_set_host_slice(self._p, items))
+
+    def set_gemm_events(self, begin: int | None, end: int | None) -> None:
+        """CUDA event handles recorded around the GEMM stage of every later run (None: off)."""
+        _check(lib().ccglib_b200_pipeline_set_gemm_events(self._p, begin, end))
 
     def run(self, d_a: int, d_b: int, d_c: int, stream: int = 0) -> None:
         _check(lib().ccglib_b200_pipeline_run(self._p, d_a, d_b, d_c, stream))

@@ -30,6 +30,7 @@ struct ccglib_b200_pipeline {
   size_t tiled_item_a, tiled_item_b;
   void *tiled_a, *tiled_b;  // pipeline-owned scratch of the device path (whole batch)
   int device;
+  cudaEvent_t ev_gemm_begin, ev_gemm_end;  // caller-owned, optional: recorded around the GEMM stage
   // host path, created by the first run_host
   size_t slice_items;
   void *slice_a[2], *slice_b[2], *slice_c[2];
@@ -95,7 +96,10 @@ int run_items(ccglib_b200_pipeline &p, const void *d_a, const void *d_b, void *d
     d_a = p.tiled_a;
     d_b = p.tiled_b;
   }
-  return run_gemm_items(p.gemm, d_a, d_b, d_c, items, stream);
+  if (p.ev_gemm_begin != nullptr) CCGLIB_CUDA_TRY(cudaEventRecord(p.ev_gemm_begin, stream));
+  const int rc = run_gemm_items(p.gemm, d_a, d_b, d_c, items, stream);
+  if (p.ev_gemm_end != nullptr) CCGLIB_CUDA_TRY(cudaEventRecord(p.ev_gemm_end, stream));
+  return rc;
 }
 
 int prepare_host_path(ccglib_b200_pipeline &p) {
@@ -244,6 +248,17 @@ extern "C" int ccglib_b200_pipeline_run(ccglib_b200_pipeline *p, const void *d_a
     return CCGLIB_B200_INVALID_ARGUMENT;
   }
   return run_items(*p, d_a, d_b, d_c, p->desc.batch, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ccglib_b200_pipeline_set_gemm_events(ccglib_b200_pipeline *p, void *begin,
+                                                    void *end) {
+  if (p == nullptr || (begin == nullptr) != (end == nullptr)) {
+    set_last_error("pipeline_set_gemm_events: give both events or neither");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  p->ev_gemm_begin = static_cast<cudaEvent_t>(begin);
+  p->ev_gemm_end = static_cast<cudaEvent_t>(end);
+  return CCGLIB_B200_OK;
 }
 
 extern "C" size_t ccglib_b200_pipeline_launches(const ccglib_b200_pipeline *p) {

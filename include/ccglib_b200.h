@@ -202,6 +202,13 @@ CCGLIB_B200_API int ccglib_b200_pipeline_run_host(ccglib_b200_pipeline *pipeline
 CCGLIB_B200_API size_t ccglib_b200_pipeline_host_slice(const ccglib_b200_pipeline *pipeline);
 CCGLIB_B200_API int ccglib_b200_pipeline_set_host_slice(ccglib_b200_pipeline *pipeline, size_t items);
 
+/* Benchmark hook: two caller-owned CUDA events (CUevent / cudaEvent_t values) that every
+ * later run records on the run's stream just before and just after the GEMM stage of the chain
+ * (for 1-bit input the stage includes the operand expansion); NULL, NULL switches it off.
+ * No counterpart in the reference. */
+CCGLIB_B200_API int ccglib_b200_pipeline_set_gemm_events(ccglib_b200_pipeline *pipeline,
+                                                         void *begin, void *end);
+
 /* Kernel launches one ccglib_b200_pipeline_run enqueues, and device bytes the pipeline owns.
  * Introspection for benchmarks; no counterpart in the reference. */
 CCGLIB_B200_API size_t ccglib_b200_pipeline_launches(const ccglib_b200_pipeline *pipeline);

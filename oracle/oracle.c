@@ -168,6 +168,16 @@ int oracle_narrow(const float *src, void *dst, size_t n, int value_type) {
   }
 }
 
+/* ---- OpenMP thread count: set explicitly, read back for the benchmark record ---- */
+
+#include <omp.h>
+
+void oracle_omp_set_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+}
+
+int oracle_omp_max_threads(void) { return omp_get_max_threads(); }
+
 /* ---- complex GEMM, floating point --------------------------------------- */
 
 /*

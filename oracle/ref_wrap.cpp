@@ -12,7 +12,16 @@
 #include <cstddef>
 #include <cstdint>
 
+#include <omp.h>
+
 #include <ccglib/gemm/reference.h>
+
+// Thread count of the OpenMP runtime the reference GEMM runs on: set explicitly (launchers such
+// as torchrun export OMP_NUM_THREADS=1) and read back, so a benchmark reports what it used.
+extern "C" void ref_omp_set_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+}
+extern "C" int ref_omp_max_threads(void) { return omp_get_max_threads(); }
 
 namespace {
 inline ccglib::mma::MemOrder order(int c_col_major) {
