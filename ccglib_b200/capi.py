@@ -20,7 +20,8 @@ OK, INVALID_ARGUMENT, UNSUPPORTED, CUDA_ERROR, DEVICE_TIMEOUT, OUT_OF_MEMORY = r
 EXPORTS = [
     "ccglib_b200_gemm_dims", "ccglib_b200_gemm_plan_create", "ccglib_b200_gemm_run",
     "ccglib_b200_gemm_plan_destroy", "ccglib_b200_gemm_plan_scratch_bytes",
-    "ccglib_b200_gemm_plan_launches",
+    "ccglib_b200_gemm_plan_launches", "ccglib_b200_gemm_plan_tile",
+    "ccglib_b200_tune_table_lookup",
     "ccglib_b200_transpose_run", "ccglib_b200_pack_run", "ccglib_b200_device_status",
     "ccglib_b200_status_string", "ccglib_b200_last_error",
     "ccglib_b200_gemm_int1_static_scratch", "ccglib_b200_selftest_wait_timeout",
@@ -85,6 +86,11 @@ def lib() -> ctypes.CDLL:
         L.ccglib_b200_gemm_plan_destroy.restype = ci
         L.ccglib_b200_gemm_plan_scratch_bytes.argtypes = [vp]
         L.ccglib_b200_gemm_plan_scratch_bytes.restype = sz
+        L.ccglib_b200_gemm_plan_tile.argtypes = [vp, ctypes.POINTER(ci * 4)]
+        L.ccglib_b200_gemm_plan_tile.restype = ci
+        L.ccglib_b200_tune_table_lookup.argtypes = [ctypes.c_char_p, ctypes.POINTER(GemmDesc),
+                                                    ctypes.POINTER(ci * 3)]
+        L.ccglib_b200_tune_table_lookup.restype = ci
         L.ccglib_b200_gemm_plan_launches.argtypes = [vp]
         L.ccglib_b200_gemm_plan_launches.restype = sz
         L.ccglib_b200_gemm_int1_static_scratch.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp]
@@ -157,6 +163,13 @@ class GemmPlan:
         """Kernel launches one run() enqueues."""
         return int(lib().ccglib_b200_gemm_plan_launches(self._plan))
 
+    @property
+    def tile(self) -> dict:
+        """Tile choice of the plan: columns, CTA pair, panel width from a table, tuned or not."""
+        t = (ctypes.c_int * 4)()
+        _check(lib().ccglib_b200_gemm_plan_tile(self._plan, ctypes.byref(t)))
+        return {"bn": int(t[0]), "pair": int(t[1]), "group_n": int(t[2]), "tuned": bool(t[3])}
+
     def run(self, d_a: int, d_b: int, d_c: int, stream: int = 0) -> None:
         _check(lib().ccglib_b200_gemm_run(self._plan, d_a, d_b, d_c, stream))
 
@@ -221,6 +234,19 @@ class Pipeline:
             self.close()
         except Exception:
             pass
+
+
+def tune_table_lookup(path: str, batch, m, n, k, type_in, type_out):
+    """(bn, pair, group_n) a tuning table file holds for a problem, or None (host only)."""
+    desc = GemmDesc(batch, m, n, k, type_in, type_out, OPT, PLANAR, ROW_MAJOR, COL_MAJOR,
+                    ROW_MAJOR, 1.0, 0.0, 0.0, 0.0)
+    choice = (ctypes.c_int * 3)()
+    status = lib().ccglib_b200_tune_table_lookup(path.encode(), ctypes.byref(desc),
+                                                 ctypes.byref(choice))
+    if status == UNSUPPORTED:
+        return None
+    _check(status)
+    return int(choice[0]), int(choice[1]), int(choice[2])
 
 
 def gemm_int1_static_scratch(batch, m, n, k, d_a, d_b, d_c, stream: int = 0, variant=BASIC,

@@ -173,6 +173,8 @@ struct ccglib_b200_gemm_plan {
   ccglib_b200_gemm_desc desc;
   KernelEntry kernel;
   int bn, sw, a_planes;
+  int group_n;            // column-panel width of the tile walk from a tuning table (0: heuristic)
+  int tuned;              // the tile choice came from a tuning table
   int max_clusters;       // CTA-pair kernels: co-resident clusters of two
   int nibbles;            // 1-bit input expanded to e2m1 nibbles (block-scaled 4-bit MMA path)
   int bytes_in;           // 1-bit input arrives as one byte per sample (Pipeline), not packed words
@@ -408,15 +410,24 @@ int ccglib_b200::create_gemm_plan(const ccglib_b200_gemm_desc *desc, const PlanO
   int bn = cost_256 <= cost_128 ? 256 : 128;
   if (cost_64 < (bn == 256 ? cost_256 : cost_128)) bn = 64;
   int sw = 128;
+  // A tuning table (CCGLIB_B200_TUNE_TABLE, written by `python -m ccglib_b200.tune --write`)
+  // overrides the model for the problems it lists; the environment overrides both.
+  TuneChoice tuned;
+  plan.tuned = tune_table_lookup(std::getenv("CCGLIB_B200_TUNE_TABLE"), d,
+                                 ceil_div<size_t>(d.k * in_bits, 8), &tuned);
+  if (!plan.tuned) tuned = TuneChoice{};
+  if (tuned.bn != 0) bn = tuned.bn;
+  plan.group_n = tuned.group_n > 0 ? tuned.group_n : 0;
+  const bool bn_forced = env_int("CCGLIB_B200_BN", 0) != 0 || tuned.bn != 0;
   bn = env_int("CCGLIB_B200_BN", bn);
   sw = env_int("CCGLIB_B200_SW", sw);
-  const bool want_pair = env_int("CCGLIB_B200_PAIR", kind == kKindMXF4 ? 1 : 0) != 0 &&
-                         d.m > kBlockM;
+  const int pair_default = tuned.pair >= 0 ? tuned.pair : (kind == kKindMXF4 ? 1 : 0);
+  const bool want_pair = env_int("CCGLIB_B200_PAIR", pair_default) != 0 && d.m > kBlockM;
   if (kind == kKindMXF4) {
     // two accumulators plus 32 scale-factor columns must fit 512 tensor-memory columns: 224
     // columns for a CTA pair (N of a 256-row MMA is a multiple of 32), else 192
     if (bn == 256) bn = 192;
-    if (want_pair && env_int("CCGLIB_B200_BN", 0) == 0) {
+    if (want_pair && !bn_forced) {
       // The pair kernel is bound by operand traffic from L2: time per 256 x bn tile goes as
       // bn / 256 + 1, and there are sms / 2 clusters.  Wider tiles move fewer bytes per flop
       // (224 columns: 8 % fewer than 192) but may quantise worse on a few waves (4096^2,
@@ -594,6 +605,18 @@ extern "C" size_t ccglib_b200_gemm_plan_scratch_bytes(const ccglib_b200_gemm_pla
   return plan != nullptr ? plan->scratch_bytes : 0;
 }
 
+extern "C" int ccglib_b200_gemm_plan_tile(const ccglib_b200_gemm_plan *plan, int tile[4]) {
+  if (plan == nullptr || tile == nullptr) {
+    set_last_error("gemm_plan_tile: null argument");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  tile[0] = plan->bn;
+  tile[1] = plan->kernel.pair ? 1 : 0;
+  tile[2] = plan->group_n;
+  tile[3] = plan->tuned;
+  return CCGLIB_B200_OK;
+}
+
 extern "C" size_t ccglib_b200_gemm_plan_launches(const ccglib_b200_gemm_plan *plan) {
   if (plan == nullptr) return 0;
   if (plan->stage_mode == kDirect) return 1;
@@ -621,8 +644,9 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
   p.tiles_n = static_cast<uint32_t>(ceil_div<size_t>(d.n, plan.bn));
   // column-panel width of the tile walk: 4 for 256-column tiles; 8 for narrower ones, except
   // on short matrices (one or two row tiles: +2 % on 256 x 2048 x 512)
-  p.group_n = static_cast<uint32_t>(
-      env_int("CCGLIB_B200_GROUP", (plan.bn == 256 || p.tiles_m <= 2) ? 4 : 8));
+  p.group_n = static_cast<uint32_t>(env_int(
+      "CCGLIB_B200_GROUP",
+      plan.group_n > 0 ? plan.group_n : ((plan.bn == 256 || p.tiles_m <= 2) ? 4 : 8)));
   if (p.group_n == 0) p.group_n = 1;
   const size_t tiles = nb * p.tiles_m * p.tiles_n;
   if (tiles > 0x7FFFFFFFull) {

@@ -113,6 +113,21 @@ CCGLIB_B200_API int ccglib_b200_gemm_plan_destroy(ccglib_b200_gemm_plan *plan);
 /* Bytes of device scratch the plan owns (0 for the direct TMA path). */
 CCGLIB_B200_API size_t ccglib_b200_gemm_plan_scratch_bytes(const ccglib_b200_gemm_plan *plan);
 
+/* Tile choice of the plan: tile = {columns per tile, 1 if a CTA pair works on a 256-row tile,
+ * column-panel width of the tile walk from a tuning table (0: built-in rule), 1 if the choice
+ * came from a tuning table}.  Introspection; no counterpart in the reference. */
+CCGLIB_B200_API int ccglib_b200_gemm_plan_tile(const ccglib_b200_gemm_plan *plan, int tile[4]);
+
+/* Look a problem up in a tuning table file (JSON written by `python -m ccglib_b200.tune
+ * --write FILE`; plans consult the file named by the environment variable
+ * CCGLIB_B200_TUNE_TABLE in the same way).  choice = {columns per tile, pair (0/1, -1 = model),
+ * column-panel width (0 = built-in rule)}; UNSUPPORTED when no entry matches (types, M, N,
+ * log2 bucket of the bytes per input row, log2 bucket of the batch).  Host only.  Takes the
+ * place of the result files of the reference's tuner (tuning/tune_gemm.py:316-363). */
+CCGLIB_B200_API int ccglib_b200_tune_table_lookup(const char *path,
+                                                  const ccglib_b200_gemm_desc *desc,
+                                                  int choice[3]);
+
 /* Kernel launches one ccglib_b200_gemm_run of this plan enqueues: 1 on the direct TMA path,
  * 3 per batch chunk (re-stage A, re-stage B, multiply) on the staged paths.  Introspection for
  * benchmarks; no counterpart in the reference. */
