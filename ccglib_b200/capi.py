@@ -21,7 +21,7 @@ EXPORTS = [
     "ccglib_b200_gemm_dims", "ccglib_b200_gemm_plan_create", "ccglib_b200_gemm_run",
     "ccglib_b200_gemm_plan_destroy", "ccglib_b200_gemm_plan_scratch_bytes",
     "ccglib_b200_gemm_plan_launches", "ccglib_b200_gemm_plan_tile",
-    "ccglib_b200_tune_table_lookup",
+    "ccglib_b200_tune_table_lookup", "ccglib_b200_batch_share",
     "ccglib_b200_transpose_run", "ccglib_b200_pack_run", "ccglib_b200_device_status",
     "ccglib_b200_status_string", "ccglib_b200_last_error",
     "ccglib_b200_gemm_int1_static_scratch", "ccglib_b200_selftest_wait_timeout",
@@ -51,6 +51,12 @@ class PipelineDesc(ctypes.Structure):
                 ("b_mem_order", ctypes.c_int), ("c_mem_order", ctypes.c_int),
                 ("alpha_re", ctypes.c_float), ("alpha_im", ctypes.c_float),
                 ("beta_re", ctypes.c_float), ("beta_im", ctypes.c_float)]
+
+
+class Share(ctypes.Structure):
+    _fields_ = [(name, ctypes.c_size_t) for name in
+                ("first", "count", "a_offset", "b_offset", "c_offset", "a_bytes", "b_bytes",
+                 "c_bytes")]
 
 
 class Error(RuntimeError):
@@ -86,11 +92,14 @@ def lib() -> ctypes.CDLL:
         L.ccglib_b200_gemm_plan_destroy.restype = ci
         L.ccglib_b200_gemm_plan_scratch_bytes.argtypes = [vp]
         L.ccglib_b200_gemm_plan_scratch_bytes.restype = sz
-        L.ccglib_b200_gemm_plan_tile.argtypes = [vp, ctypes.POINTER(ci * 4)]
+        L.ccglib_b200_gemm_plan_tile.argtypes = [vp, ctypes.POINTER(ci * 5)]
         L.ccglib_b200_gemm_plan_tile.restype = ci
         L.ccglib_b200_tune_table_lookup.argtypes = [ctypes.c_char_p, ctypes.POINTER(GemmDesc),
                                                     ctypes.POINTER(ci * 3)]
         L.ccglib_b200_tune_table_lookup.restype = ci
+        L.ccglib_b200_batch_share.argtypes = [ctypes.POINTER(GemmDesc), ci, ci,
+                                              ctypes.POINTER(Share)]
+        L.ccglib_b200_batch_share.restype = ci
         L.ccglib_b200_gemm_plan_launches.argtypes = [vp]
         L.ccglib_b200_gemm_plan_launches.restype = sz
         L.ccglib_b200_gemm_int1_static_scratch.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp]
@@ -166,9 +175,10 @@ class GemmPlan:
     @property
     def tile(self) -> dict:
         """Tile choice of the plan: columns, CTA pair, panel width from a table, tuned or not."""
-        t = (ctypes.c_int * 4)()
+        t = (ctypes.c_int * 5)()
         _check(lib().ccglib_b200_gemm_plan_tile(self._plan, ctypes.byref(t)))
-        return {"bn": int(t[0]), "pair": int(t[1]), "group_n": int(t[2]), "tuned": bool(t[3])}
+        return {"bn": int(t[0]), "pair": int(t[1]), "group_n": int(t[2]), "tuned": bool(t[3]),
+                "split_k": int(t[4])}
 
     def run(self, d_a: int, d_b: int, d_c: int, stream: int = 0) -> None:
         _check(lib().ccglib_b200_gemm_run(self._plan, d_a, d_b, d_c, stream))
@@ -234,6 +244,17 @@ class Pipeline:
             self.close()
         except Exception:
             pass
+
+
+def batch_share(batch, m, n, k, type_in, type_out, variant, world, rank) -> dict:
+    """Rank's contiguous share of a batch split over `world` devices (host arithmetic)."""
+    desc = GemmDesc(batch, m, n, k, type_in, type_out, variant, PLANAR, ROW_MAJOR, COL_MAJOR,
+                    ROW_MAJOR, 1.0, 0.0, 0.0, 0.0)
+    share = Share()
+    _check(lib().ccglib_b200_batch_share(ctypes.byref(desc), world, rank, ctypes.byref(share)))
+    keys = {"first": "first", "count": "count", "a": "a_offset", "b": "b_offset",
+            "c": "c_offset", "a_bytes": "a_bytes", "b_bytes": "b_bytes", "c_bytes": "c_bytes"}
+    return {k: int(getattr(share, v)) for k, v in keys.items()}
 
 
 def tune_table_lookup(path: str, batch, m, n, k, type_in, type_out):

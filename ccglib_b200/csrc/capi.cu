@@ -53,7 +53,7 @@ namespace {
 
 struct TuneEntry {
   long long type_in = -1, type_out = -1, m = -1, n = -1, k_bucket = -1, batch_bucket = -1;
-  long long bn = 0, pair = -1, group_n = 0;
+  long long bn = 0, pair = -1, group_n = 0, split_k = 0;
 };
 
 unsigned log2_bucket(size_t v) {
@@ -107,6 +107,7 @@ bool parse_table(const std::string &text, std::vector<TuneEntry> &out) {
       else if (key == "bn") e.bn = value;
       else if (key == "pair") e.pair = value;
       else if (key == "group_n") e.group_n = value;
+      else if (key == "split_k") e.split_k = value;
     }
     out.push_back(e);
     i = end + 1;
@@ -136,6 +137,7 @@ int tune_table_lookup(const char *path, const ccglib_b200_gemm_desc &d, size_t k
       choice->bn = static_cast<int>(e.bn);
       choice->pair = static_cast<int>(e.pair);
       choice->group_n = static_cast<int>(e.group_n);
+      choice->split_k = static_cast<int>(e.split_k);
       return 1;
     }
   }
@@ -196,3 +198,59 @@ extern "C" const char *ccglib_b200_status_string(int status) {
 }
 
 extern "C" const char *ccglib_b200_last_error(void) { return g_last_error; }
+
+namespace {
+size_t value_bits(int t) {
+  switch (t) {
+  case CCGLIB_B200_INT1: return 1;
+  case CCGLIB_B200_FLOAT8E4M3:
+  case CCGLIB_B200_FLOAT8E5M2: return 8;
+  case CCGLIB_B200_BFLOAT16:
+  case CCGLIB_B200_FLOAT16: return 16;
+  case CCGLIB_B200_INT32:
+  case CCGLIB_B200_FLOAT32: return 32;
+  default: return 0;
+  }
+}
+} // namespace
+
+// Batch items are independent GEMMs and the batch is the outermost axis of every layout, so the
+// share of one device is a contiguous slice of A, B and C: pure host arithmetic.
+extern "C" int ccglib_b200_batch_share(const ccglib_b200_gemm_desc *desc, int world, int rank,
+                                       ccglib_b200_share *out) {
+  if (desc == nullptr || out == nullptr || world < 1 || rank < 0 || rank >= world) {
+    set_last_error("batch_share: need a description, world >= 1 and 0 <= rank < world");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  const size_t in_bits = value_bits(desc->type_in), out_bits = value_bits(desc->type_out);
+  if (in_bits == 0 || out_bits == 0 || desc->type_in == CCGLIB_B200_INT32) {
+    set_last_error("batch_share: unsupported value types (%d -> %d)", desc->type_in,
+                   desc->type_out);
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  const size_t w = static_cast<size_t>(world), r = static_cast<size_t>(rank);
+  const size_t base = desc->batch / w, extra = desc->batch % w;
+  out->count = base + (r < extra ? 1 : 0);          // the first batch % world ranks take one more
+  out->first = r * base + (r < extra ? r : extra);
+  size_t a_item, b_item;
+  if (desc->variant == CCGLIB_B200_OPT) {
+    unsigned dims[3];
+    const int rc = ccglib_b200_gemm_dims(desc->type_in, desc->type_out, desc->variant, dims);
+    if (rc != CCGLIB_B200_OK) return rc;
+    const size_t kp = ceil_div<size_t>(desc->k, dims[2]) * dims[2];
+    a_item = 2 * ceil_div<size_t>(desc->m, dims[0]) * dims[0] * kp * in_bits / 8;
+    b_item = 2 * ceil_div<size_t>(desc->n, dims[1]) * dims[1] * kp * in_bits / 8;
+  } else {
+    const size_t row = in_bits == 1 ? ceil_div<size_t>(desc->k, 32) * 4 : desc->k * in_bits / 8;
+    a_item = 2 * desc->m * row;
+    b_item = 2 * desc->n * row;
+  }
+  const size_t c_item = 2 * desc->m * desc->n * out_bits / 8;
+  out->a_offset = out->first * a_item;
+  out->b_offset = out->first * b_item;
+  out->c_offset = out->first * c_item;
+  out->a_bytes = out->count * a_item;
+  out->b_bytes = out->count * b_item;
+  out->c_bytes = out->count * c_item;
+  return CCGLIB_B200_OK;
+}

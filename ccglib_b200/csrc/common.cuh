@@ -56,10 +56,11 @@ int launch_pad_rows(const void *d_in, void *d_out, size_t rows, size_t row_bytes
 
 // One entry of a tuning table (see capi.cu): tile width in columns (0 = leave to the model), one
 // CTA or a CTA pair per tile (-1 = leave to the model), column-panel width of the tile walk
-// (0 = leave to the model).  Looked up by (types, M, N, log2 bucket of the row bytes, log2 bucket
+// (0 = leave to the model), split-K factor.  Looked up by (types, M, N, log2 bucket of the row bytes, log2 bucket
 // of the batch); returns 1 when an entry matched.
 struct TuneChoice {
   int bn = 0, pair = -1, group_n = 0;
+  int split_k = 0;  // CTAs sharing the K of one tile (0 = leave to the model)
 };
 int tune_table_lookup(const char *path, const ccglib_b200_gemm_desc &d, size_t k_bytes,
                       TuneChoice *choice);

@@ -10,6 +10,7 @@
 #include <new>
 
 #include "gemm_kernels.cuh"
+#include "gemm_splitk.cuh"
 
 namespace ccglib_b200 {
 
@@ -76,6 +77,7 @@ struct KernelEntry {
   int smem;
   bool epi_tma;  // the instance reserves staging tiles for the TMA-store epilogue
   bool pair;     // CTA-pair kernel: launched as clusters of two, tiles are 256 rows high
+  int split;     // split-K kernel: clusters of `split` CTAs per 128 x 128 tile (else 1)
 };
 
 // Four-byte outputs get the TMA-store epilogue wherever its 32 KiB of staging costs no pipeline
@@ -84,13 +86,22 @@ template <int KIND, int BN, int SW, int A_PLANES, typename OutT, int DEPTH = 2>
 KernelEntry entry() {
   constexpr int kEpi = (sizeof(OutT) == 4 && !(A_PLANES == 3 && BN == 256)) ? DEPTH : 0;
   return {cgemm_tcgen05_kernel<KIND, BN, SW, A_PLANES, OutT, kEpi>,
-          Cfg<BN, SW, A_PLANES, kEpi>::kSmemBytes, kEpi > 0, false};
+          Cfg<BN, SW, A_PLANES, kEpi>::kSmemBytes, kEpi > 0, false, 1};
+}
+
+// Split-K instances exist for float32 output of the floating-point kinds.
+template <int KIND> KernelEntry splitk_entry(int split) {
+  if (split == 4) {
+    return {cgemm_splitk_kernel<KIND, 4, float, true>, SplitCfg<4, true>::kSmemBytes, true, false,
+            4};
+  }
+  return {cgemm_splitk_kernel<KIND, 2, float, true>, SplitCfg<2, true>::kSmemBytes, true, false, 2};
 }
 
 template <int KIND, int BN, int A_PLANES, typename OutT, bool EPI_TMA = (sizeof(OutT) == 4)>
 KernelEntry pair_entry() {
   return {cgemm_pair_kernel<KIND, BN, A_PLANES, OutT, EPI_TMA>,
-          PairCfg<BN, A_PLANES, EPI_TMA>::kSmemBytes, EPI_TMA, true};
+          PairCfg<BN, A_PLANES, EPI_TMA>::kSmemBytes, EPI_TMA, true, 1};
 }
 
 template <int KIND, int A_PLANES, typename OutT>
@@ -117,7 +128,7 @@ template <int KIND> KernelEntry pick_float_out(int type_out, int bn, int sw, boo
   case CCGLIB_B200_BFLOAT16:
     return pick_tile<KIND, 2, __nv_bfloat16>(bn, sw, pair);
   default:
-    return {nullptr, 0, false, false};
+    return {nullptr, 0, false, false, 1};
   }
 }
 
@@ -465,9 +476,45 @@ int ccglib_b200::create_gemm_plan(const ccglib_b200_gemm_desc *desc, const PlanO
   // The 4-bit path is the exception: it is bound by operand traffic from L2, not by power, and a
   // pair halves the B bytes each SM fetches (5.6 against 5.3 POPS at 4096 x 4096 x 65536).
   const bool pair = want_pair && sw == 128 && bn != 64;
+  // Split-K for problems that leave most SMs idle: when even 128 x 128 tiles fill less than half
+  // (a quarter) of the device and K is long enough to share, a cluster of 2 (4) CTAs per tile
+  // shortens the MMA chain per SM and moves fewer operand bytes out of L2 than narrower tiles
+  // would (1024^3, batch 1: 64 tiles x 2 CTAs instead of 128 tiles of 128 x 64).
+  int split = 1;
+  {
+    const size_t tiles128 = tiles_m * ceil_div<size_t>(d.n, 128);
+    const size_t k_blocks = ceil_div<size_t>(plan.k_bytes, 128);
+    const bool can_split = kind != kKindI8 && kind != kKindMXF4 &&
+                           d.type_out == CCGLIB_B200_FLOAT32 && !pair && sw == 128 &&
+                           !bn_forced;
+    if (can_split && 4 * tiles128 <= sms && k_blocks >= 16) {
+      split = 4;
+    } else if (can_split && 2 * tiles128 <= sms && k_blocks >= 8) {
+      split = 2;
+    }
+    if (tuned.split_k > 0) split = tuned.split_k;
+    split = env_int("CCGLIB_B200_SPLITK", split);
+    if (split != 1 && split != 2 && split != 4) {
+      set_last_error("CCGLIB_B200_SPLITK must be 1, 2 or 4");
+      return CCGLIB_B200_INVALID_ARGUMENT;
+    }
+    if (split > 1 && (kind == kKindI8 || kind == kKindMXF4 || d.type_out != CCGLIB_B200_FLOAT32 ||
+                      k_blocks < static_cast<size_t>(split))) {
+      split = 1;  // no such instance: integer sums, 16-bit output, or less K than CTAs
+    }
+  }
+  if (split > 1) {
+    bn = 128;
+    sw = 128;
+  }
   plan.bn = bn;
   plan.sw = sw;
-  switch (kind) {
+  switch (split > 1 ? -1 : kind) {
+  case -1:
+    plan.kernel = kind == kKindF16    ? splitk_entry<kKindF16>(split)
+                  : kind == kKindTF32 ? splitk_entry<kKindTF32>(split)
+                                      : splitk_entry<kKindF8F6F4>(split);
+    break;
   case kKindF16:
     plan.kernel = pick_float_out<kKindF16>(d.type_out, bn, sw, pair);
     break;
@@ -605,7 +652,7 @@ extern "C" size_t ccglib_b200_gemm_plan_scratch_bytes(const ccglib_b200_gemm_pla
   return plan != nullptr ? plan->scratch_bytes : 0;
 }
 
-extern "C" int ccglib_b200_gemm_plan_tile(const ccglib_b200_gemm_plan *plan, int tile[4]) {
+extern "C" int ccglib_b200_gemm_plan_tile(const ccglib_b200_gemm_plan *plan, int tile[5]) {
   if (plan == nullptr || tile == nullptr) {
     set_last_error("gemm_plan_tile: null argument");
     return CCGLIB_B200_INVALID_ARGUMENT;
@@ -614,6 +661,7 @@ extern "C" int ccglib_b200_gemm_plan_tile(const ccglib_b200_gemm_plan *plan, int
   tile[1] = plan->kernel.pair ? 1 : 0;
   tile[2] = plan->group_n;
   tile[3] = plan->tuned;
+  tile[4] = plan->kernel.split;
   return CCGLIB_B200_OK;
 }
 
@@ -740,6 +788,27 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    CCGLIB_CUDA_TRY(cudaLaunchKernelEx(&cfg, plan.kernel.fn, tm_a, tm_b, tm_c, p));
+    return CCGLIB_B200_OK;
+  }
+  if (plan.kernel.split > 1) {
+    // one cluster per tile (not persistent); clusters beyond the co-resident ones run as they fit
+    if (tiles * plan.kernel.split > 0x7FFFFFFFull) {
+      set_last_error("gemm_run: too many tiles for the split-K form");
+      return CCGLIB_B200_INVALID_ARGUMENT;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(tiles * plan.kernel.split));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = plan.kernel.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = static_cast<unsigned>(plan.kernel.split);
     attr.val.clusterDim.y = 1;
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;

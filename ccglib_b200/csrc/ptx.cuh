@@ -174,6 +174,23 @@ __device__ __forceinline__ void st_shared_cluster_u32(uint32_t addr_cluster, uin
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr_cluster), "r"(v) : "memory");
 }
 
+// 16-byte store to a shared::cluster address (another CTA's shared memory) and 16-byte load from
+// this CTA's own shared memory.
+__device__ __forceinline__ void st_shared_cluster_v4(uint32_t addr_cluster, uint32_t a, uint32_t b,
+                                                     uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr_cluster), "r"(a),
+               "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
+__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t &a, uint32_t &b, uint32_t &c,
+                                             uint32_t &d) {
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
+               : "r"(addr)
+               : "memory");
+}
+
 // Arrive (and add expected bytes) on an mbarrier given by a shared::cluster address.
 __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t bar_cluster, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(

@@ -115,8 +115,9 @@ CCGLIB_B200_API size_t ccglib_b200_gemm_plan_scratch_bytes(const ccglib_b200_gem
 
 /* Tile choice of the plan: tile = {columns per tile, 1 if a CTA pair works on a 256-row tile,
  * column-panel width of the tile walk from a tuning table (0: built-in rule), 1 if the choice
- * came from a tuning table}.  Introspection; no counterpart in the reference. */
-CCGLIB_B200_API int ccglib_b200_gemm_plan_tile(const ccglib_b200_gemm_plan *plan, int tile[4]);
+ * came from a tuning table, CTAs that share the K of one tile (split-K; 1 = none)}.
+ * Introspection; no counterpart in the reference. */
+CCGLIB_B200_API int ccglib_b200_gemm_plan_tile(const ccglib_b200_gemm_plan *plan, int tile[5]);
 
 /* Look a problem up in a tuning table file (JSON written by `python -m ccglib_b200.tune
  * --write FILE`; plans consult the file named by the environment variable
@@ -255,6 +256,24 @@ CCGLIB_B200_API int ccglib_b200_pipeline_destroy(ccglib_b200_pipeline *pipeline)
 CCGLIB_B200_API int ccglib_b200_gemm_int1_static_scratch(const ccglib_b200_gemm_desc *desc,
                                                          const void *d_a, const void *d_b,
                                                          void *d_c, void *stream);
+
+/*
+ * Multi-GPU help.  Batch items are independent GEMMs and the batch is the outermost axis of
+ * every layout, so a batch is spread over the GPUs of a node by giving each a contiguous slice;
+ * nothing is exchanged between devices.  For device `rank` of `world`: the first item and the
+ * number of items of its share (as even as possible, the first batch % world ranks take one
+ * more), and where that share starts in whole-batch A, B and C arrays laid out as `desc` says
+ * (basic or opt layout).  The caller creates one plan per device with batch = count.  Host only.
+ * The reference has no multi-GPU support; no counterpart.
+ */
+typedef struct ccglib_b200_share {
+  size_t first, count;
+  size_t a_offset, b_offset, c_offset; /* bytes */
+  size_t a_bytes, b_bytes, c_bytes;
+} ccglib_b200_share;
+
+CCGLIB_B200_API int ccglib_b200_batch_share(const ccglib_b200_gemm_desc *desc, int world,
+                                            int rank, ccglib_b200_share *share);
 
 /* Read and clear the sticky device-side status word of the current device (synchronises the
  * device).  Non-zero means a bounded wait inside a kernel gave up; its results are invalid. */

@@ -296,6 +296,28 @@ def test_baseline_shapes_fp64_gate(case):
     print("%s accumulation error / (sqrt(2K) u S) = %.3f" % (case[0], ratio))
 
 
+@pytest.mark.parametrize("types", [(ou.F16, ou.F32), (ou.BF16, ou.F32), (ou.F32, ou.F32),
+                                   (ou.E4M3, ou.F32)], ids=["f16", "bf16", "tf32", "e4m3"])
+def test_same_sign_inputs_show_the_truncation_bias_and_stay_inside_the_gate(types):
+    """All-positive operands make the running sum of the imaginary part grow to |c|; the tensor
+    core's truncating adder then loses a fraction of a unit in the last place per MMA
+    instruction, always downwards.  The gate's bias term covers it; the measured share of that
+    term is printed (it is what DESIGN quotes)."""
+    type_in, type_out = types
+    B, M, N, K = 1, 256, 256, 4096
+    a, b = make_inputs(71, type_in, B, M, N, K, dist="unit")
+    got = gu.run_gemm(type_in, type_out, a, b, B, M, N, K).reshape(B, 2, M, N)
+    gu.assert_close_fp64(got, type_in, type_out, a, b, K)
+    c64, s = ou.double_gemm(type_in, a[0], b[0])
+    im_err = got[0, 1].astype(np.float64) - c64[1]
+    steps = 2.0 * K / gu.MMA_K[type_in]
+    share = np.abs(im_err) / (steps * 2.0 ** -23 * np.abs(c64[1]))
+    print("%s: bias %.3g of |c| (mean signed error %.3g), %.2f of the gate's bias term at most" % (
+        ou.TYPE_NAMES[type_in], float(np.abs(im_err).max() / np.abs(c64[1]).max()),
+        float(im_err.mean()), float(share.max())))
+    assert float(im_err.mean()) <= 0.0  # truncation: never above the exact sum on positive data
+
+
 def test_int1_config3_k65536_bit_exact():
     # BASELINE config 3's K (65536 bits) on one 128 x 256 output tile per batch item
     B, M, N, K = 2, 128, 256, 65536

@@ -36,6 +36,25 @@ def test_item_bytes_match_the_layouts():
     assert a == 2 * 384 * 128 * 2 and b == 2 * 256 * 128 * 2 and c == 2 * 300 * 200 * 4
 
 
+def test_c_abi_share_equals_the_python_helper():
+    """ccglib_b200_batch_share (what a C or C++ caller uses) against ccglib_b200.sharding."""
+    from ccglib_b200 import capi
+
+    cases = [(64, 8192, 8192, 8192, capi.FLOAT16, capi.FLOAT32, capi.OPT, 16, 32),
+             (7, 300, 200, 100, capi.FLOAT16, capi.FLOAT16, capi.OPT, 16, 16),
+             (5, 40, 72, 70, capi.INT1, capi.INT32, capi.BASIC, 1, 32),
+             (32, 4096, 4096, 16384, capi.FLOAT8E4M3, capi.FLOAT32, capi.BASIC, 8, 32)]
+    for batch, m, n, k, tin, tout, variant, in_bits, out_bits in cases:
+        dims = capi.gemm_dims(tin, tout, variant)
+        for world in (1, 2, 3, 8):
+            for rank in range(world):
+                want = sharding.byte_offsets(batch, world, rank, m, n, k, in_bits, out_bits,
+                                             tiled=variant == capi.OPT, dims=dims)
+                assert capi.batch_share(batch, m, n, k, tin, tout, variant, world, rank) == want
+    with pytest.raises(capi.Error):
+        capi.batch_share(4, 8, 8, 8, capi.FLOAT16, capi.FLOAT32, capi.BASIC, 2, 2)
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

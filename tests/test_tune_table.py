@@ -58,6 +58,9 @@ def test_table_entry_overrides_the_model_with_identical_results(tmp_path, monkey
 
     type_in, type_out = types
     B, M, N, K = 3, 300, 520, 1056
+    # compare tile forms only: split-K (which the model would pick for so few tiles) adds the
+    # partial sums of the K shares in another order
+    monkeypatch.setenv("CCGLIB_B200_SPLITK", "1")
     a, b = make_inputs(61, type_in, B, M, N, K)
     d_a, d_b = gu.dev(a), gu.dev(b)
     c_bytes = B * 2 * M * N * 4
@@ -80,7 +83,7 @@ def test_table_entry_overrides_the_model_with_identical_results(tmp_path, monkey
     monkeypatch.setenv("CCGLIB_B200_TUNE_TABLE", _table(tmp_path, [entry]))
     tuned_tile, c_tuned = run()
     assert tuned_tile == {"bn": other_bn, "pair": 1 - model_tile["pair"], "group_n": 3,
-                          "tuned": True}
+                          "tuned": True, "split_k": 1}
     # each element still sums its K products in the same order: identical bits
     assert torch.equal(c_model, c_tuned)
     got = gu.host(c_tuned, ou.STORAGE[type_out]).reshape(B, 2, M, N)
