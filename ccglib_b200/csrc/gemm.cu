@@ -479,7 +479,10 @@ int ccglib_b200::create_gemm_plan(const ccglib_b200_gemm_desc *desc, const PlanO
   // Split-K for problems that leave most SMs idle: when even 128 x 128 tiles fill less than half
   // (a quarter) of the device and K is long enough to share, a cluster of 2 (4) CTAs per tile
   // shortens the MMA chain per SM and moves fewer operand bytes out of L2 than narrower tiles
-  // would (1024^3, batch 1: 64 tiles x 2 CTAs instead of 128 tiles of 128 x 64).
+  // would (1024^3, batch 1: 64 tiles x 2 CTAs instead of 128 tiles of 128 x 64).  The exchange
+  // costs about 4 us per call, a K-block about 0.35 us less per CTA: measured on 1024 x 1024,
+  // f16, split 2 against 128 x 64 tiles: K = 512 14.3 against 12.3 us, K = 1024 16.4 against
+  // 18.4 us, K = 4096 33.7 against 53.2 us.
   int split = 1;
   {
     const size_t tiles128 = tiles_m * ceil_div<size_t>(d.n, 128);
@@ -487,9 +490,9 @@ int ccglib_b200::create_gemm_plan(const ccglib_b200_gemm_desc *desc, const PlanO
     const bool can_split = kind != kKindI8 && kind != kKindMXF4 &&
                            d.type_out == CCGLIB_B200_FLOAT32 && !pair && sw == 128 &&
                            !bn_forced;
-    if (can_split && 4 * tiles128 <= sms && k_blocks >= 16) {
+    if (can_split && 4 * tiles128 <= sms && k_blocks >= 24) {
       split = 4;
-    } else if (can_split && 2 * tiles128 <= sms && k_blocks >= 8) {
+    } else if (can_split && 2 * tiles128 <= sms && k_blocks >= 12) {
       split = 2;
     }
     if (tuned.split_k > 0) split = tuned.split_k;

@@ -161,6 +161,40 @@ __device__ __forceinline__ void bytes4(uint32_t bits, int valid, uint32_t &pos, 
   neg = (0x01010101u + y * 0xFEu) & mask;
 }
 
+// 4 one-byte samples -> the low nibble of each byte holds the e2m1 code of the sample:
+// non-zero = +1.0 = 0x2, zero = -1.0 = 0xA (high nibbles are 0).
+__device__ __forceinline__ uint32_t nibble_codes4(uint32_t w) {
+  const uint32_t nz = ((w & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | w;  // bit 7 of a byte: byte != 0
+  return ((~nz >> 4) & 0x08080808u) | 0x02020202u;
+}
+
+// 16 samples of one plane (one 16-byte piece) -> 16 nibbles, sample j in nibble j.
+__device__ __forceinline__ uint2 nibbles_of_piece(const uint4 &x) {
+  uint32_t t[4];
+  const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint32_t v = nibble_codes4(w[q]);
+    t[q] = v | (v >> 4);  // byte 0 = samples 0, 1; byte 2 = samples 2, 3
+  }
+  return make_uint2(__byte_perm(t[0], t[1], 0x6420u), __byte_perm(t[2], t[3], 0x6420u));
+}
+
+// 8 (re, im) pairs (one 16-byte piece of interleaved input) -> 8 real and 8 imaginary nibbles.
+__device__ __forceinline__ void nibbles_of_pairs(const uint4 &x, uint32_t &re, uint32_t &im) {
+  uint32_t t[4];
+  const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint32_t v = nibble_codes4(w[q]);  // bytes: re0, im0, re1, im1
+    t[q] = v | (v >> 12);                    // byte 0 = re0 | re1 << 4, byte 1 = im0 | im1 << 4
+  }
+  const uint32_t lo = __byte_perm(t[0], t[1], 0x5140u);  // re(t0), re(t1), im(t0), im(t1)
+  const uint32_t hi = __byte_perm(t[2], t[3], 0x5140u);
+  re = __byte_perm(lo, hi, 0x5410u);
+  im = __byte_perm(lo, hi, 0x7632u);
+}
+
 struct ExpandBytesParams {
   const uint8_t *in;
   int8_t *out;
@@ -197,6 +231,10 @@ __global__ void __launch_bounds__(256) expand_bytes_warp_kernel(const ExpandByte
   int8_t *out_row = p.out + ((b * p.planes_out + c) * p.rows + r) * p.out_row_bytes;
   const uint8_t *in_row = INTERLEAVED ? p.in + (b * p.rows + r) * p.k * 2
                                       : p.in + ((b * 2 + c) * p.rows + r) * p.k;
+  // full pieces of nibble output take the direct route (about two integer operations per
+  // sample, so that the pass stays bound by memory); ragged tails and the signed-byte form go
+  // through the bit masks
+  uint4 raw[4];
   uint32_t re[4], im[4];
   int valid[4];
 #pragma unroll
@@ -207,15 +245,18 @@ __global__ void __launch_bounds__(256) expand_bytes_warp_kernel(const ExpandByte
                    ? static_cast<int>(p.k - k0 < kSamples ? p.k - k0 : kSamples)
                    : 0;
     re[i] = im[i] = 0;
+    raw[i] = make_uint4(0, 0, 0, 0);
     if (valid[i] == kSamples && p.vec_ok) {
-      const uint4 x = __ldg(reinterpret_cast<const uint4 *>(in_row) + u);
-      if constexpr (INTERLEAVED) {
-        re[i] = squeeze4(__byte_perm(x.x, x.y, 0x6420u)) |
-                (squeeze4(__byte_perm(x.z, x.w, 0x6420u)) << 4);
-        im[i] = squeeze4(__byte_perm(x.x, x.y, 0x7531u)) |
-                (squeeze4(__byte_perm(x.z, x.w, 0x7531u)) << 4);
-      } else {
-        re[i] = squeeze16(x);
+      raw[i] = __ldg(reinterpret_cast<const uint4 *>(in_row) + u);
+      if constexpr (!NIBBLES) {
+        if constexpr (INTERLEAVED) {
+          re[i] = squeeze4(__byte_perm(raw[i].x, raw[i].y, 0x6420u)) |
+                  (squeeze4(__byte_perm(raw[i].z, raw[i].w, 0x6420u)) << 4);
+          im[i] = squeeze4(__byte_perm(raw[i].x, raw[i].y, 0x7531u)) |
+                  (squeeze4(__byte_perm(raw[i].z, raw[i].w, 0x7531u)) << 4);
+        } else {
+          re[i] = squeeze16(raw[i]);
+        }
       }
     } else {
       for (int j = 0; j < valid[i]; ++j) {
@@ -233,6 +274,25 @@ __global__ void __launch_bounds__(256) expand_bytes_warp_kernel(const ExpandByte
     const size_t u = blk * 128 + i * 32 + lane;
     if (u >= p.pieces) continue;
     int8_t *dst = out_row + u * kOutBytes;
+    if constexpr (NIBBLES) {
+      if (valid[i] == kSamples && p.vec_ok) {
+        if constexpr (INTERLEAVED) {
+          uint32_t r, m;
+          nibbles_of_pairs(raw[i], r, m);
+          *reinterpret_cast<uint32_t *>(dst) = r;
+          *reinterpret_cast<uint32_t *>(dst + plane_bytes) = m;
+          if (p.planes_out == 3) *reinterpret_cast<uint32_t *>(dst + 2 * plane_bytes) = m ^ 0x88888888u;
+        } else {
+          const uint2 v = nibbles_of_piece(raw[i]);
+          *reinterpret_cast<uint2 *>(dst) = v;
+          if (p.planes_out == 3 && c == 1) {
+            *reinterpret_cast<uint2 *>(dst + plane_bytes) =
+                make_uint2(v.x ^ 0x88888888u, v.y ^ 0x88888888u);
+          }
+        }
+        continue;
+      }
+    }
     // plane `c` from re[]; with interleaved input also plane 1 from im[]
 #pragma unroll
     for (int part = 0; part < (INTERLEAVED ? 2 : 1); ++part) {
