@@ -758,6 +758,12 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
   p.prefetch = static_cast<uint32_t>(env_int("CCGLIB_B200_PREFETCH", 0));
   // TMA-store epilogue: row-major C (planar or interleaved), four-byte elements, 16-byte aligned rows
   p.epi_tma = (plan.kernel.epi_tma && p.vec_ok && plan.out_elem_bytes == 4) ? 1u : 0u;
+  // experiment: planar row-major four-byte C straight from registers in full sectors
+  p.epi_direct = (env_int("CCGLIB_B200_EPI_DIRECT", 0) != 0 && planar && row && p.vec_ok &&
+                  plan.out_elem_bytes == 4 && !pair && plan.kernel.split == 1)
+                     ? 1u
+                     : 0u;
+  if (p.epi_direct) p.epi_tma = 0;
   if (!maps_cached) {
     if (p.epi_tma) {
       const size_t row_bytes = planar ? d.n * 4 : d.n * 8;
