@@ -1,6 +1,7 @@
 """Ahead-of-time build of the CUDA library (sm_100a only) into ccglib_b200/lib/.
 
     python -m ccglib_b200.build [--force]
+    python -m ccglib_b200.build --trace     # instrumented copy in ccglib_b200/lib/trace/
 
 The shared library links the CUDA runtime statically and resolves the one driver entry point it
 needs (cuTensorMapEncodeTiled) at run time, so it loads on machines without a GPU driver too.
@@ -50,6 +51,29 @@ def _compile(src: str, verbose: bool) -> str:
     return obj
 
 
+def build_trace() -> str:
+    """Instrumented copy of the library (-DCCGLIB_B200_TRACE: the GEMM kernel stamps the SM clock
+    at tile start, last MMA issued, accumulator complete and epilogue done, see
+    `python -m ccglib_b200.tune --timeline`).  Selected with CCGLIB_B200_LIB; never the default."""
+    out_dir = os.path.join(LIB_DIR, "trace")
+    obj_dir = os.path.join(out_dir, "obj")
+    os.makedirs(obj_dir, exist_ok=True)
+    objs = []
+
+    def one(src):
+        obj = os.path.join(obj_dir, os.path.splitext(src)[0] + ".o")
+        subprocess.run([NVCC] + NVCC_FLAGS + ["-DCCGLIB_B200_TRACE", "-c",
+                                              os.path.join(CSRC, src), "-o", obj], check=True)
+        return obj
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
+        objs = list(pool.map(one, SOURCES))
+    path = os.path.join(out_dir, "libccglib_b200.so")
+    subprocess.run([NVCC, "-shared", "-o", path] + objs +
+                   ["-gencode", "arch=compute_100a,code=sm_100a"], check=True)
+    return path
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale(LIB_PATH, _deps()):
         return LIB_PATH
@@ -62,4 +86,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--trace" in sys.argv:
+        print(build_trace())
+    else:
+        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

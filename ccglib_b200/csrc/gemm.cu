@@ -758,12 +758,6 @@ int launch_gemm(const ccglib_b200_gemm_plan &plan, const void *a, const void *b,
   p.prefetch = static_cast<uint32_t>(env_int("CCGLIB_B200_PREFETCH", 0));
   // TMA-store epilogue: row-major C (planar or interleaved), four-byte elements, 16-byte aligned rows
   p.epi_tma = (plan.kernel.epi_tma && p.vec_ok && plan.out_elem_bytes == 4) ? 1u : 0u;
-  // experiment: planar row-major four-byte C straight from registers in full sectors
-  p.epi_direct = (env_int("CCGLIB_B200_EPI_DIRECT", 0) != 0 && planar && row && p.vec_ok &&
-                  plan.out_elem_bytes == 4 && !pair && plan.kernel.split == 1)
-                     ? 1u
-                     : 0u;
-  if (p.epi_direct) p.epi_tma = 0;
   if (!maps_cached) {
     if (p.epi_tma) {
       const size_t row_bytes = planar ? d.n * 4 : d.n * 8;
@@ -966,6 +960,18 @@ extern "C" int ccglib_b200_device_status(unsigned *word) {
   *word = value;
   return value == 0 ? CCGLIB_B200_OK : CCGLIB_B200_DEVICE_TIMEOUT;
 }
+
+#ifdef CCGLIB_B200_TRACE
+// Instrumented builds only: copy the clock stamps out (and clear them).
+extern "C" __attribute__((visibility("default"))) int ccglib_b200_debug_trace_read(
+    long long *host, size_t count) {
+  const size_t all = sizeof(g_trace) / sizeof(long long);
+  if (host == nullptr || count > all) return CCGLIB_B200_INVALID_ARGUMENT;
+  CCGLIB_CUDA_TRY(cudaDeviceSynchronize());
+  CCGLIB_CUDA_TRY(cudaMemcpyFromSymbol(host, g_trace, count * sizeof(long long)));
+  return CCGLIB_B200_OK;
+}
+#endif
 
 // ------------------------------------------------------------------------------------------
 // Self-test of the time-out machinery: a wait that is guaranteed to run out, made on the host

@@ -34,6 +34,22 @@ namespace ccglib_b200 {
 // Sticky device-side status word: kernels OR a code into it when a bounded wait gives up.
 __device__ unsigned int g_device_status = 0;
 
+#ifdef CCGLIB_B200_TRACE
+// Instrumented builds only (-DCCGLIB_B200_TRACE; never in the shipped library): SM clock stamps of
+// the first tiles of every CTA of cgemm_tcgen05_kernel: [0] tile start at the MMA issuer,
+// [1] last MMA issued, [2] accumulator complete at the epilogue, [3] epilogue done.
+constexpr int kTraceTiles = 48;
+__device__ long long g_trace[160][kTraceTiles][4];
+#define CCGLIB_TRACE(iter, slot)                                                         \
+  do {                                                                                   \
+    if ((iter) < kTraceTiles && blockIdx.x < 160) g_trace[blockIdx.x][(iter)][(slot)] = clock64(); \
+  } while (0)
+#else
+#define CCGLIB_TRACE(iter, slot) \
+  do {                           \
+  } while (0)
+#endif
+
 namespace {
 
 using namespace ptx;
@@ -64,7 +80,6 @@ struct GemmParams {
   uint32_t c_layout;
   uint32_t have_alpha, have_beta, vec_ok;
   uint32_t epi_tma;  // stage C through shared memory and store it with TMA (row-major, 4-byte)
-  uint32_t epi_direct;  // planar row-major 4-byte C straight from registers in full 32-byte sectors
   uint32_t prefetch;  // k-blocks the producer asks L2 to fetch ahead of its own loads (0 = off)
   float alpha_re, alpha_im, beta_re, beta_im;
   unsigned int *status;
@@ -413,73 +428,6 @@ __device__ __forceinline__ void epilogue_chunk_staged(const GemmParams &p, const
   }
 }
 
-// Epilogue for 32 rows (first row m0, the warp's TMEM lanes at t_lane) and 32 columns from n0 of
-// planar row-major C with four-byte elements, stored straight from registers: the accumulators
-// are read in the 16x256b fragment shape, in which four threads hold 32 contiguous bytes of a
-// row, so every store instruction writes eight full 32-byte sectors and nothing goes through
-// shared memory.  Needs N % 2 == 0 and 8-byte aligned rows (vec_ok covers both).
-template <typename OutT>
-__device__ __forceinline__ void epilogue_chunk_direct(const GemmParams &p, uint32_t lane,
-                                                      uint32_t b, uint32_t m0, uint32_t n0,
-                                                      uint32_t t_re, uint32_t t_im) {
-  using Tr = OutTraits<OutT>;
-  using Acc = typename Tr::Acc;
-  static_assert(sizeof(OutT) == 4, "direct sector stores are for four-byte outputs");
-  OutT *C = static_cast<OutT *>(p.c);
-  const size_t plane = static_cast<size_t>(p.M) * p.N;
-  const size_t base = static_cast<size_t>(b) * 2 * plane;
-#pragma unroll
-  for (uint32_t h = 0; h < 2; ++h) {
-    uint32_t re[16], im[16];
-    tmem_ld_16x256b_x4(t_re + ((16 * h) << 16), re);
-    tmem_ld_16x256b_x4(t_im + ((16 * h) << 16), im);
-    tmem_wait_ld();
-#pragma unroll
-    for (uint32_t i = 0; i < 4; ++i) {
-      const uint32_t n = n0 + 8 * i + 2 * (lane & 3);
-      if (n >= p.N) continue;
-#pragma unroll
-      for (uint32_t rr = 0; rr < 2; ++rr) {
-        const uint32_t m = m0 + 16 * h + (lane >> 2) + 8 * rr;
-        if (m >= p.M) continue;
-        Acc vr[2], vi[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          vr[e] = Tr::from_bits(re[4 * i + 2 * rr + e]);
-          vi[e] = Tr::from_bits(im[4 * i + 2 * rr + e]);
-        }
-        OutT *c_re = C + base + static_cast<size_t>(m) * p.N + n;
-        OutT *c_im = c_re + plane;
-        if (p.have_alpha) {
-          const Acc ar = static_cast<Acc>(p.alpha_re), ai = static_cast<Acc>(p.alpha_im);
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const Acc r = vr[e];
-            vr[e] = ar * r - ai * vi[e];
-            vi[e] = ai * r + ar * vi[e];
-          }
-        }
-        if (p.have_beta) {
-          const Acc br = static_cast<Acc>(p.beta_re), bi = static_cast<Acc>(p.beta_im);
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const Acc cr = Tr::to_acc(c_re[e]), ci = Tr::to_acc(c_im[e]);
-            vr[e] += br * cr - bi * ci;
-            vi[e] += bi * cr + br * ci;
-          }
-        }
-        uint2 q_re, q_im;
-        q_re.x = Packer<OutT>::word(&vr[0]);
-        q_re.y = Packer<OutT>::word(&vr[1]);
-        q_im.x = Packer<OutT>::word(&vi[0]);
-        q_im.y = Packer<OutT>::word(&vi[1]);
-        *reinterpret_cast<uint2 *>(c_re) = q_re;
-        *reinterpret_cast<uint2 *>(c_im) = q_im;
-      }
-    }
-  }
-}
-
 template <int KIND, int BN, int SW, int A_PLANES, typename OutT, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
@@ -634,12 +582,14 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     // ------------------------------------------------------------------ MMA issuer
     uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
     bool ok = true;
-    for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+    [[maybe_unused]] uint32_t iter = 0;
+    for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++iter) {
       if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1, abort_flag, p.status,
                      kDevTimeoutMma, p.wait_cycles)) {
         break;
       }
       tc_fence_after();
+      if (lane == 0) CCGLIB_TRACE(iter, 0);
       const uint32_t d_re = tmem_base + acc * (2 * BN);
       const uint32_t d_im = d_re + BN;
       for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
@@ -684,7 +634,10 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             }
           }
           tc_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs have read it
-          if (kb + 1 == p.k_blocks) tc_commit(bar_acc_full + 8 * acc);
+          if (kb + 1 == p.k_blocks) {
+            tc_commit(bar_acc_full + 8 * acc);
+            CCGLIB_TRACE(iter, 1);
+          }
         }
         __syncwarp();
         if (++stage == kStages) {
@@ -702,26 +655,21 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     const uint32_t quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
     uint32_t acc = 0, acc_phase = 0;
     uint32_t slot = 0;  // staging tile rotation
-    for (uint32_t tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+    [[maybe_unused]] uint32_t iter = 0;
+    for (uint32_t tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++iter) {
       const TileCoord t = decode_tile(p, tile);
       if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, p.status,
                      kDevTimeoutEpilogue, p.wait_cycles)) {
         break;
       }
       tc_fence_after();
+      if (warp == 2 && lane == 0) CCGLIB_TRACE(iter, 2);
       const uint32_t m = t.mt * kBlockM + quad * 32 + lane;
       const uint32_t t_re = tmem_base + ((quad * 32) << 16) + acc * (2 * BN);
 #pragma unroll 1
       for (uint32_t c0 = 0; c0 < BN; c0 += 32) {
         const uint32_t n0 = t.nt * BN + c0;
         if (n0 >= p.N) break;
-        if constexpr (sizeof(OutT) == 4) {
-          if (p.epi_direct) {
-            epilogue_chunk_direct<OutT>(p, lane, t.b, t.mt * kBlockM + quad * 32, n0, t_re + c0,
-                                        t_re + BN + c0);
-            continue;
-          }
-        }
         uint32_t bits_re[32], bits_im[32];
         tmem_ld_32x32b_x32(t_re + c0, bits_re);
         tmem_ld_32x32b_x32(t_re + BN + c0, bits_im);
@@ -740,6 +688,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
       tc_fence_before();
       __syncwarp();
+      if (warp == 2 && lane == 0) CCGLIB_TRACE(iter, 3);
       if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
       if (++acc == kAccStages) {
         acc = 0;

@@ -9,6 +9,8 @@ board's power cap binds.
     python -m ccglib_b200.tune --b 4096 --m 256 --n 2048 --k 512 --precision_in bfloat16 --data random
     python -m ccglib_b200.tune ... --write table.json     # store the winner for the plan to use
     python -m ccglib_b200.tune ... --ncu                  # print the ncu command for one launch
+    CCGLIB_B200_LIB=ccglib_b200/lib/trace/libccglib_b200.so \
+        python -m ccglib_b200.tune ... --timeline         # per-tile clock stamps (instrumented build)
 
 Every form is selected through the same environment variables a user can set for a deployment
 (CCGLIB_B200_BN, CCGLIB_B200_PAIR, CCGLIB_B200_GROUP); torch only provides device memory, streams
@@ -103,6 +105,50 @@ def _operands(args, tin, row_bytes):
     return out[0], out[1]
 
 
+def _timeline(args, tin, tout, d_a, d_b, d_c, stream) -> int:
+    """Mean per-tile intervals, in SM clock cycles, over the CTAs of one launch: how long the MMA
+    issuer is held by a tile, how long until its accumulator is complete, how long the epilogue
+    takes and how much of it delays the next tile."""
+    import ctypes
+
+    import numpy as np
+    import torch
+
+    lib = capi.lib()
+    if not hasattr(lib, "ccglib_b200_debug_trace_read"):
+        print("this library has no clock stamps: build it with `python -m ccglib_b200.build "
+              "--trace` and select it with CCGLIB_B200_LIB", file=sys.stderr)
+        return 1
+    plan = capi.GemmPlan(args.b, args.m, args.n, args.k, tin, tout, variant=capi.BASIC)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        plan.run(d_a.data_ptr(), d_b.data_ptr(), d_c.data_ptr(), stream)
+    e0.record()
+    plan.run(d_a.data_ptr(), d_b.data_ptr(), d_c.data_ptr(), stream)
+    e1.record()
+    torch.cuda.synchronize()
+    n = 160 * 48 * 4
+    buf = (ctypes.c_longlong * n)()
+    lib.ccglib_b200_debug_trace_read.argtypes = [ctypes.c_void_p, ctypes.c_size_t]
+    if lib.ccglib_b200_debug_trace_read(buf, n) != 0:
+        return 1
+    t = np.frombuffer(buf, dtype=np.int64).reshape(160, 48, 4)
+    t = t[(t[:, 40, 0] > 0)][:, 2:40]  # CTAs that ran at least 41 tiles; skip the first two
+    if t.shape[0] == 0:
+        print("too few tiles per CTA for a timeline (need more than 40)", file=sys.stderr)
+        return 1
+    ms = e0.elapsed_time(e1)
+    print("%s: %.3f ms, %.1f TOps/s, %d CTAs traced" % (plan.tile, ms,
+          8e-9 * args.b * args.m * args.n * args.k / ms, t.shape[0]))
+    print("tile period at the MMA issuer          %8.0f clk" % (t[:, 1:, 0] - t[:, :-1, 0]).mean())
+    print("tile start -> last MMA issued          %8.0f clk" % (t[:, :, 1] - t[:, :, 0]).mean())
+    print("tile start -> accumulator complete     %8.0f clk" % (t[:, :, 2] - t[:, :, 0]).mean())
+    print("epilogue (accumulator complete -> free) %7.0f clk" % (t[:, :, 3] - t[:, :, 2]).mean())
+    print("last MMA issued -> next tile may start %8.0f clk" % (t[:, 1:, 0] - t[:, :-1, 1]).mean())
+    plan.close()
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m ccglib_b200.tune")
     ap.add_argument("--b", type=int, default=1)
@@ -118,6 +164,10 @@ def main(argv=None) -> int:
                     help="merge the fastest form into this tuning table (JSON)")
     ap.add_argument("--ncu", action="store_true",
                     help="print the ncu command for a single-launch capture and exit")
+    ap.add_argument("--timeline", action="store_true",
+                    help="per-tile timeline of the plan's choice from the clock stamps of an "
+                         "instrumented library (python -m ccglib_b200.build --trace, selected "
+                         "with CCGLIB_B200_LIB)")
     ap.add_argument("--single", action="store_true",
                     help="one warm-up and one launch of the plan's choice, nothing else "
                          "(the program an ncu capture runs)")
@@ -144,6 +194,8 @@ def main(argv=None) -> int:
     d_c = torch.empty(args.b * 2 * args.m * args.n * BITS[tout] // 8, dtype=torch.uint8,
                       device="cuda")
     stream = int(torch.cuda.current_stream().cuda_stream)
+    if args.timeline:
+        return _timeline(args, tin, tout, d_a, d_b, d_c, stream)
     if args.single:
         plan = capi.GemmPlan(args.b, args.m, args.n, args.k, tin, tout, variant=capi.BASIC)
         for _ in range(2):
