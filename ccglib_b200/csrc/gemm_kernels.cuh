@@ -879,12 +879,14 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
     if (rank == 0) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      for (uint32_t tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
+      [[maybe_unused]] uint32_t iter = 0;
+      for (uint32_t tile = pair; ok && tile < p.num_tiles; tile += num_pairs, ++iter) {
         if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1, abort_flag, p.status,
                        kDevTimeoutMma, p.wait_cycles, peer_abort)) {
           break;
         }
         tc_fence_after();
+        if (lane == 0) CCGLIB_TRACE(iter, 0);
         const uint32_t d_re = tmem_base + acc * (2 * BN);
         const uint32_t d_im = d_re + BN;
         for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
@@ -933,6 +935,7 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
             if (kb + 1 == p.k_blocks) {
               tc_commit_pair(map_to_cta(bar_acc_full + 8 * acc, 0));
               tc_commit_pair(map_to_cta(bar_acc_full + 8 * acc, 1));
+              CCGLIB_TRACE(iter, 1);
             }
           }
           __syncwarp();
@@ -952,13 +955,15 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
     const uint32_t quad = warp & 3;
     uint32_t acc = 0, acc_phase = 0;
     uint32_t slot = 0;
-    for (uint32_t tile = pair; tile < p.num_tiles; tile += num_pairs) {
+    [[maybe_unused]] uint32_t iter = 0;
+    for (uint32_t tile = pair; tile < p.num_tiles; tile += num_pairs, ++iter) {
       const TileCoord t = decode_tile(p, tile);
       if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, abort_flag, p.status,
-                     kDevTimeoutEpilogue, p.wait_cycles)) {
+                     kDevTimeoutEpilogue, p.wait_cycles, peer_abort)) {
         break;
       }
       tc_fence_after();
+      if (rank == 0 && warp == 2 && lane == 0) CCGLIB_TRACE(iter, 2);
       const uint32_t m0 = (t.mt * 2 + rank) * kBlockM + quad * 32;
       const uint32_t t_re = tmem_base + ((quad * 32) << 16) + acc * (2 * BN);
 #pragma unroll 1
@@ -981,6 +986,7 @@ cgemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
       tc_fence_before();
       __syncwarp();
+      if (rank == 0 && warp == 2 && lane == 0) CCGLIB_TRACE(iter, 3);
       if (lane == 0) mbar_arrive_cluster(map_to_cta(bar_acc_empty + 8 * acc, 0));
       if (++acc == kAccStages) {
         acc = 0;

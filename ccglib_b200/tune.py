@@ -133,7 +133,7 @@ def _timeline(args, tin, tout, d_a, d_b, d_c, stream) -> int:
     if lib.ccglib_b200_debug_trace_read(buf, n) != 0:
         return 1
     t = np.frombuffer(buf, dtype=np.int64).reshape(160, 48, 4)
-    t = t[(t[:, 40, 0] > 0)][:, 2:40]  # CTAs that ran at least 41 tiles; skip the first two
+    t = t[(t[:, 40, 0] > 0)][:, 2:40]  # (leader) CTAs that ran at least 41 tiles; skip the first two
     if t.shape[0] == 0:
         print("too few tiles per CTA for a timeline (need more than 40)", file=sys.stderr)
         return 1
