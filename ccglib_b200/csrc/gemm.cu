@@ -5,6 +5,7 @@
 //
 // Replaces ccglib::mma::GEMM (reference src/mma/GEMM.cpp:56-108,231-275) and its per-type kernel
 // tables (src/mma/Kernel.cpp:7-73).
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -643,6 +644,19 @@ int ccglib_b200::create_gemm_plan(const ccglib_b200_gemm_desc *desc, const PlanO
     }
   }
 
+  if (env_int("CCGLIB_B200_VERBOSE", 0) != 0) {
+    // the counterpart of the reference's DEBUG print of its launch geometry (src/mma/GEMM.cpp:84-95)
+    std::fprintf(stderr,
+                 "ccglib_b200 plan: batch %zu M %zu N %zu K %zu types %d->%d variant %d | tile %d x "
+                 "%d, stage rows %d B, %s%s, split-K %d, %s | staging mode %d, %d lane(s), chunk "
+                 "%zu item(s), scratch %zu bytes | shared memory %d B, %d SMs\n",
+                 d.batch, d.m, d.n, d.k, d.type_in, d.type_out, d.variant,
+                 plan.kernel.pair ? 2 * kBlockM : kBlockM, plan.bn, plan.sw,
+                 plan.kernel.pair ? "CTA pair" : "one CTA", plan.nibbles ? ", e2m1 operands" : "",
+                 plan.kernel.split, plan.tuned ? "from the tuning table" : "built-in model",
+                 plan.stage_mode, plan.lanes, plan.batch_chunk, plan.scratch_bytes,
+                 plan.kernel.smem, plan.sms);
+  }
   *out = new (std::nothrow) ccglib_b200_gemm_plan(plan);
   if (*out == nullptr) {
     release_plan_resources(plan);

@@ -478,3 +478,12 @@ def test_run_twice_same_plan_is_deterministic():
     torch.cuda.synchronize()
     gu.check_device_status()
     assert torch.equal(d_c1, d_c2)
+
+
+def test_verbose_prints_the_plan_geometry(monkeypatch, capfd):
+    # the counterpart of the reference's DEBUG print of its launch geometry (src/mma/GEMM.cpp:84-95)
+    monkeypatch.setenv("CCGLIB_B200_VERBOSE", "1")
+    plan = capi.GemmPlan(2, 300, 520, 1056, ou.INT1, ou.INT32, variant=capi.BASIC)
+    plan.close()
+    err = capfd.readouterr().err
+    assert "ccglib_b200 plan: batch 2 M 300 N 520 K 1056" in err and "CTA pair" in err
