@@ -11,7 +11,11 @@ import oracle_util as ou
 from ccglib_b200 import capi
 from test_gpu_gemm import make_inputs
 
+import os
+
 pytestmark = pytest.mark.gpu
+# cases per fuzz test; CCGLIB_B200_FUZZ_CASES raises it for a soak run
+CASES = int(os.environ.get("CCGLIB_B200_FUZZ_CASES", "40"))
 
 EDGES = [1, 7, 63, 64, 65, 127, 128, 129, 191, 192, 193, 223, 224, 225, 255, 256, 257, 300, 448,
          449, 511, 513, 640]
@@ -65,7 +69,7 @@ def _run(case):
     return got, want, a, b
 
 
-@pytest.mark.parametrize("case", _cases(17, 40, [(ou.INT1, ou.INT32)]),
+@pytest.mark.parametrize("case", _cases(17, CASES, [(ou.INT1, ou.INT32)]),
                          ids=lambda c: "i1-%d-B%d-%dx%dx%d" % (c[0], c[3], c[4], c[5], c[6]))
 def test_int1_random_shapes_bit_exact(case):
     got, want, _, _ = _run(case)
@@ -76,7 +80,7 @@ FLOATS = [(ou.F16, ou.F32), (ou.BF16, ou.F32), (ou.F32, ou.F32), (ou.E4M3, ou.F3
           (ou.E5M2, ou.F32), (ou.F16, ou.F16), (ou.BF16, ou.BF16), (ou.F32, ou.F16)]
 
 
-@pytest.mark.parametrize("case", _cases(23, 40, FLOATS),
+@pytest.mark.parametrize("case", _cases(23, CASES, FLOATS),
                          ids=lambda c: "%s-%d-B%d-%dx%dx%d" % (ou.TYPE_NAMES[c[1]], c[0], c[3],
                                                                 c[4], c[5], c[6]))
 def test_float_random_shapes_reference_rule(case):
@@ -84,3 +88,78 @@ def test_float_random_shapes_reference_rule(case):
     gu.assert_close_reference_rule(got, want, case[1], case[2])
     if not case[-1]:  # alpha = 1, beta = 0: the library's own, much tighter, gate applies as well
         gu.assert_close_fp64(got, case[1], case[2], a, b, case[6])
+
+
+def _pipeline_cases(seed, count):
+    rng = np.random.default_rng(seed)
+    out = []
+    for i in range(count):
+        one_bit = bool(rng.integers(2))
+        M = int(rng.choice(EDGES))
+        N = int(rng.choice(EDGES))
+        K = int(rng.choice([16, 24, 40, 70, 256, 1000, 1056, 2080] if one_bit
+                           else [8, 40, 64, 100, 264, 520, 1100]))
+        B = int(rng.choice([1, 2, 3, 5]))
+        in_axis = capi.INTERLEAVED if rng.integers(2) else capi.PLANAR
+        out_axis = capi.INTERLEAVED if rng.integers(2) else capi.PLANAR
+        c_order = capi.COL_MAJOR if rng.integers(2) else capi.ROW_MAJOR
+        host = bool(rng.integers(2))
+        slice_items = int(rng.integers(1, B + 1))
+        out.append((i, one_bit, B, M, N, K, in_axis, out_axis, c_order, host, slice_items))
+    return out
+
+
+@pytest.mark.parametrize("case", _pipeline_cases(29, max(20, CASES // 2)),
+                         ids=lambda c: "%s-%d-B%d-%dx%dx%d-%s" % ("i1" if c[1] else "f16", c[0], c[2],
+                                                                 c[3], c[4], c[5],
+                                                                 "host" if c[9] else "dev"))
+def test_pipeline_random_shapes(case):
+    """The Pipeline on seeded random shapes: 1-bit byte samples or f16, planar or interleaved
+    input and output, row- or col-major C, device operands or host operands cut into slices."""
+    import torch
+
+    i, one_bit, B, M, N, K, in_axis, out_axis, c_order, host, slice_items = case
+    rng = np.random.default_rng(3000 + i)
+    if one_bit:
+        a = rng.integers(0, 2, (B, 2, M, K)).astype(np.uint8) * rng.integers(1, 256, (B, 2, M, K)).astype(np.uint8)
+        b = rng.integers(0, 2, (B, 2, N, K)).astype(np.uint8)
+        kw = -(-K // 32)
+        def packed(x, rows):
+            padded = np.zeros((B, 2, rows, kw * 32), np.uint8)
+            padded[..., :K] = x != 0
+            return np.packbits(padded, axis=-1, bitorder="little").view(np.uint32).reshape(
+                B, 2, rows, kw)
+        want = gu.oracle_batch(ou.INT1, ou.INT32, packed(a, M), packed(b, N), B, M, N, K)
+        tin, tout, out_dt = ou.INT1, ou.INT32, np.int32
+    else:
+        a = ou.random_storage(rng, (B, 2, M, K), ou.F16, "uniform")
+        b = ou.random_storage(rng, (B, 2, N, K), ou.F16, "uniform")
+        want = gu.oracle_batch(ou.F16, ou.F32, a, b, B, M, N, K)
+        tin, tout, out_dt = ou.F16, ou.F32, np.float32
+    a_in = np.ascontiguousarray(a.transpose(0, 2, 3, 1)) if in_axis == capi.INTERLEAVED else a
+    b_in = np.ascontiguousarray(b.transpose(0, 2, 3, 1)) if in_axis == capi.INTERLEAVED else b
+    pipe = capi.Pipeline(B, M, N, K, tin, tout, variant=capi.OPT, input_complex_axis=in_axis,
+                         output_complex_axis=out_axis, c_mem_order=c_order)
+    c_bytes = B * 2 * M * N * 4
+    if host:
+        pipe.host_slice = slice_items
+        h_a, h_b = np.ascontiguousarray(a_in), np.ascontiguousarray(b_in)
+        h_c = np.full(B * 2 * M * N, 0x5A5A5A5A, np.uint32)
+        pipe.run_host(h_a.ctypes.data, h_b.ctypes.data, h_c.ctypes.data, gu.stream_handle())
+        raw = h_c.view(out_dt)
+    else:
+        d_a, d_b = gu.dev(a_in), gu.dev(b_in)
+        d_c = gu.dev_empty(c_bytes + 512, 0x5A)
+        pipe.run(d_a.data_ptr(), d_b.data_ptr(), d_c.data_ptr() + 256, gu.stream_handle())
+        torch.cuda.synchronize()
+        whole = d_c.cpu().numpy()
+        assert np.all(whole[:256] == 0x5A) and np.all(whole[256 + c_bytes:] == 0x5A)
+        raw = whole[256:256 + c_bytes].view(out_dt)
+    gu.check_device_status()
+    pipe.close()
+    got = gu.canonical_c(raw, B, M, N, out_axis, c_order)
+    if one_bit:
+        assert np.array_equal(got, want)
+    else:
+        gu.assert_close_reference_rule(got, want, tin, tout)
+        gu.assert_close_fp64(got, tin, tout, a, b, K)

@@ -302,7 +302,7 @@ def test_same_sign_inputs_show_the_truncation_bias_and_stay_inside_the_gate(type
     """All-positive operands make the running sum of the imaginary part grow to |c|; the tensor
     core's truncating adder then loses a fraction of a unit in the last place per MMA
     instruction, always downwards.  The gate's bias term covers it; the measured share of that
-    term is printed (it is what DESIGN quotes)."""
+    term is printed."""
     type_in, type_out = types
     B, M, N, K = 1, 256, 256, 4096
     a, b = make_inputs(71, type_in, B, M, N, K, dist="unit")

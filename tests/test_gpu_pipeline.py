@@ -49,6 +49,10 @@ INT1_CASES = [
      dict(CCGLIB_B200_INT1_MXF4="0")),
     ("three-nibble-planes", 2, 300, 260, 2048, capi.INTERLEAVED, capi.PLANAR, capi.OPT,
      dict(CCGLIB_B200_MXF4_NEGATE="0")),
+    ("three-nibble-planes-planar-in", 2, 260, 300, 2064, capi.PLANAR, capi.INTERLEAVED, capi.BASIC,
+     dict(CCGLIB_B200_MXF4_NEGATE="0")),
+    ("single-cta-unaligned-base", 1, 100, 96, 48, capi.PLANAR, capi.PLANAR, capi.OPT,
+     dict(CCGLIB_B200_PAIR="0")),
 ]
 
 
