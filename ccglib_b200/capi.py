@@ -28,7 +28,7 @@ EXPORTS = [
     "ccglib_b200_pipeline_create", "ccglib_b200_pipeline_run", "ccglib_b200_pipeline_run_host",
     "ccglib_b200_pipeline_host_slice", "ccglib_b200_pipeline_set_host_slice",
     "ccglib_b200_pipeline_launches", "ccglib_b200_pipeline_scratch_bytes",
-    "ccglib_b200_pipeline_set_gemm_events",
+    "ccglib_b200_pipeline_set_gemm_events", "ccglib_b200_pipeline_set_overlap",
     "ccglib_b200_pipeline_destroy",
 ]
 
@@ -125,6 +125,8 @@ def lib() -> ctypes.CDLL:
         L.ccglib_b200_pipeline_set_host_slice.restype = ci
         L.ccglib_b200_pipeline_set_gemm_events.argtypes = [vp, vp, vp]
         L.ccglib_b200_pipeline_set_gemm_events.restype = ci
+        L.ccglib_b200_pipeline_set_overlap.argtypes = [vp, ci]
+        L.ccglib_b200_pipeline_set_overlap.restype = ci
         L.ccglib_b200_pipeline_launches.argtypes = [vp]
         L.ccglib_b200_pipeline_launches.restype = sz
         L.ccglib_b200_pipeline_scratch_bytes.argtypes = [vp]
@@ -222,6 +224,11 @@ class Pipeline:
     @host_slice.setter
     def host_slice(self, items: int) -> None:
         _check(lib().ccglib_b200_pipeline_set_host_slice(self._p, items))
+
+    def set_overlap(self, on: bool) -> None:
+        """Transposes of later batch chunks beside the GEMM of earlier ones (default) or the
+        plain chain on the caller's stream."""
+        _check(lib().ccglib_b200_pipeline_set_overlap(self._p, 1 if on else 0))
 
     def set_gemm_events(self, begin: int | None, end: int | None) -> None:
         """CUDA event handles recorded around the GEMM stage of every later run (None: off)."""

@@ -14,11 +14,16 @@
 // Replaces ccglib::pipeline::Pipeline (reference src/pipeline/Pipeline.cpp:44-126 for the chain
 // and the scratch ownership, :162-188 for the two Run forms), whose chain is
 // Packing -> Transpose -> GEMM as separate passes over HBM.
+#include <cstdlib>
 #include <new>
 
 #include "common.cuh"
 
 using namespace ccglib_b200;
+
+namespace {
+constexpr int kMaxChunks = 8;
+}
 
 struct ccglib_b200_pipeline {
   ccglib_b200_pipeline_desc desc;
@@ -31,6 +36,12 @@ struct ccglib_b200_pipeline {
   void *tiled_a, *tiled_b;  // pipeline-owned scratch of the device path (whole batch)
   int device;
   cudaEvent_t ev_gemm_begin, ev_gemm_end;  // caller-owned, optional: recorded around the GEMM stage
+  // device path with tiling: the batch goes in chunks, the transposes of later chunks running on
+  // a side stream beside the GEMM of earlier ones
+  size_t chunk_items;
+  bool overlap_on;  // ccglib_b200_pipeline_set_overlap
+  cudaStream_t s_side;
+  cudaEvent_t ev_call, ev_tiled[kMaxChunks];
   // host path, created by the first run_host
   size_t slice_items;
   void *slice_a[2], *slice_b[2], *slice_c[2];
@@ -76,28 +87,74 @@ void release(ccglib_b200_pipeline &p) {
     if (p.slice_a[0] != nullptr) cudaFree(p.slice_a[0]);
     p.host_ready = false;
   }
+  if (p.s_side != nullptr) {
+    cudaStreamSynchronize(p.s_side);
+    cudaStreamDestroy(p.s_side);
+    p.s_side = nullptr;
+  }
+  if (p.ev_call != nullptr) cudaEventDestroy(p.ev_call);
+  p.ev_call = nullptr;
+  for (cudaEvent_t &e : p.ev_tiled) {
+    if (e != nullptr) cudaEventDestroy(e);
+    e = nullptr;
+  }
   if (p.tiled_a != nullptr) cudaFree(p.tiled_a);
   p.tiled_a = p.tiled_b = nullptr;
   if (p.gemm != nullptr) ccglib_b200_gemm_plan_destroy(p.gemm);
   p.gemm = nullptr;
 }
 
-// The chain on `items` batch items of device operands, all on `stream`.
+// The chain on `items` batch items of device operands.  Everything is ordered after what
+// `stream` holds at the call and before what is enqueued on it afterwards.  With tiling and a
+// batch of several chunks the transposes run on the pipeline's side stream, chunk by chunk, and
+// the GEMM of a chunk waits only for its own operands: the transposes (bound by HBM bandwidth)
+// of later chunks then run beside the GEMM (bound by the tensor cores and the power cap) of
+// earlier ones instead of in front of it.
 int run_items(ccglib_b200_pipeline &p, const void *d_a, const void *d_b, void *d_c, size_t items,
               cudaStream_t stream) {
   const ccglib_b200_pipeline_desc &d = p.desc;
-  if (p.tiles) {
-    int rc = ccglib_b200_transpose_run(items, d.m, d.k, p.m_blk, p.k_c, p.bits,
-                                       d.input_complex_axis, d_a, p.tiled_a, stream);
-    if (rc != CCGLIB_B200_OK) return rc;
-    rc = ccglib_b200_transpose_run(items, d.n, d.k, p.n_blk, p.k_c, p.bits, d.input_complex_axis,
-                                   d_b, p.tiled_b, stream);
-    if (rc != CCGLIB_B200_OK) return rc;
-    d_a = p.tiled_a;
-    d_b = p.tiled_b;
+  if (!p.tiles) {
+    if (p.ev_gemm_begin != nullptr) CCGLIB_CUDA_TRY(cudaEventRecord(p.ev_gemm_begin, stream));
+    const int rc = run_gemm_items(p.gemm, d_a, d_b, d_c, items, stream);
+    if (p.ev_gemm_end != nullptr) CCGLIB_CUDA_TRY(cudaEventRecord(p.ev_gemm_end, stream));
+    return rc;
   }
-  if (p.ev_gemm_begin != nullptr) CCGLIB_CUDA_TRY(cudaEventRecord(p.ev_gemm_begin, stream));
-  const int rc = run_gemm_items(p.gemm, d_a, d_b, d_c, items, stream);
+  const size_t chunk =
+      (p.s_side != nullptr && p.overlap_on && p.chunk_items < items) ? p.chunk_items : items;
+  const bool overlap = chunk < items;
+  cudaStream_t s_t = overlap ? p.s_side : stream;
+  if (overlap) {
+    // the side stream starts after everything the caller enqueued so far, which includes the
+    // GEMMs of an earlier call that may still be reading the tiled buffers
+    CCGLIB_CUDA_TRY(cudaEventRecord(p.ev_call, stream));
+    CCGLIB_CUDA_TRY(cudaStreamWaitEvent(s_t, p.ev_call, 0));
+  }
+  int rc = CCGLIB_B200_OK;
+  size_t ci = 0;
+  for (size_t b0 = 0; b0 < items && rc == CCGLIB_B200_OK; b0 += chunk, ++ci) {
+    const size_t nb = items - b0 < chunk ? items - b0 : chunk;
+    char *ta = static_cast<char *>(p.tiled_a) + b0 * p.tiled_item_a;
+    char *tb = static_cast<char *>(p.tiled_b) + b0 * p.tiled_item_b;
+    rc = ccglib_b200_transpose_run(nb, d.m, d.k, p.m_blk, p.k_c, p.bits, d.input_complex_axis,
+                                   static_cast<const char *>(d_a) + b0 * p.item_a, ta, s_t);
+    if (rc != CCGLIB_B200_OK) break;
+    rc = ccglib_b200_transpose_run(nb, d.n, d.k, p.n_blk, p.k_c, p.bits, d.input_complex_axis,
+                                   static_cast<const char *>(d_b) + b0 * p.item_b, tb, s_t);
+    if (rc != CCGLIB_B200_OK) break;
+    if (overlap) {
+      CCGLIB_CUDA_TRY(cudaEventRecord(p.ev_tiled[ci], s_t));
+      CCGLIB_CUDA_TRY(cudaStreamWaitEvent(stream, p.ev_tiled[ci], 0));
+    }
+    if (ci == 0 && p.ev_gemm_begin != nullptr) {
+      CCGLIB_CUDA_TRY(cudaEventRecord(p.ev_gemm_begin, stream));
+    }
+    rc = run_gemm_items(p.gemm, ta, tb, static_cast<char *>(d_c) + b0 * p.item_c, nb, stream);
+  }
+  if (overlap) {
+    // after a failed launch the caller's stream must still come after the side stream
+    CCGLIB_CUDA_TRY(cudaEventRecord(p.ev_call, s_t));
+    CCGLIB_CUDA_TRY(cudaStreamWaitEvent(stream, p.ev_call, 0));
+  }
   if (p.ev_gemm_end != nullptr) CCGLIB_CUDA_TRY(cudaEventRecord(p.ev_gemm_end, stream));
   return rc;
 }
@@ -167,6 +224,7 @@ extern "C" int ccglib_b200_pipeline_create(const ccglib_b200_pipeline_desc *desc
 
   ccglib_b200_pipeline p{};
   p.desc = d;
+  p.overlap_on = true;
   CCGLIB_CUDA_TRY(cudaGetDevice(&p.device));
   ccglib_b200_gemm_desc g{};
   g.batch = d.batch;
@@ -218,6 +276,26 @@ extern "C" int ccglib_b200_pipeline_create(const ccglib_b200_pipeline_desc *desc
       return CCGLIB_B200_OUT_OF_MEMORY;
     }
     p.tiled_b = static_cast<char *>(p.tiled_a) + bytes_a;
+    // chunks of at least 2e13 operations (some ten milliseconds of GEMM), at most kMaxChunks
+    const double ops_item = 8.0 * static_cast<double>(d.m) * d.n * d.k;
+    size_t chunk = static_cast<size_t>(2e13 / ops_item) + 1;
+    const char *forced = std::getenv("CCGLIB_B200_PIPE_CHUNK");  // items per chunk (experiments)
+    if (forced != nullptr && std::atoi(forced) > 0) chunk = static_cast<size_t>(std::atoi(forced));
+    if (chunk < ceil_div<size_t>(d.batch, kMaxChunks)) chunk = ceil_div<size_t>(d.batch, kMaxChunks);
+    p.chunk_items = chunk;
+    const char *env = std::getenv("CCGLIB_B200_PIPE_OVERLAP");
+    const bool want = env == nullptr || *env == '\0' || std::atoi(env) != 0;
+    if (want && chunk < d.batch) {
+      cudaError_t err = cudaStreamCreateWithFlags(&p.s_side, cudaStreamNonBlocking);
+      if (err == cudaSuccess) err = cudaEventCreateWithFlags(&p.ev_call, cudaEventDisableTiming);
+      for (cudaEvent_t &e : p.ev_tiled) {
+        if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
+      }
+      if (err != cudaSuccess) {
+        release(p);
+        return cuda_fail(err, "creating the side stream of the pipeline");
+      }
+    }
   }
   // host path: slices of about 1 GiB of the larger of input and output, at least one item
   const size_t per_item = (p.item_a + p.item_b > p.item_c) ? p.item_a + p.item_b : p.item_c;
@@ -261,9 +339,21 @@ extern "C" int ccglib_b200_pipeline_set_gemm_events(ccglib_b200_pipeline *p, voi
   return CCGLIB_B200_OK;
 }
 
+extern "C" int ccglib_b200_pipeline_set_overlap(ccglib_b200_pipeline *p, int on) {
+  if (p == nullptr) {
+    set_last_error("pipeline_set_overlap: null argument");
+    return CCGLIB_B200_INVALID_ARGUMENT;
+  }
+  p->overlap_on = on != 0;
+  return CCGLIB_B200_OK;
+}
+
 extern "C" size_t ccglib_b200_pipeline_launches(const ccglib_b200_pipeline *p) {
   if (p == nullptr) return 0;
-  return ccglib_b200_gemm_plan_launches(p->gemm) + (p->tiles ? 2 : 0);
+  if (!p->tiles) return ccglib_b200_gemm_plan_launches(p->gemm);
+  const size_t chunks =
+      (p->s_side != nullptr && p->overlap_on) ? ceil_div(p->desc.batch, p->chunk_items) : 1;
+  return chunks * (2 + ccglib_b200_gemm_plan_launches(p->gemm));
 }
 
 extern "C" size_t ccglib_b200_pipeline_scratch_bytes(const ccglib_b200_pipeline *p) {

@@ -218,6 +218,14 @@ CCGLIB_B200_API int ccglib_b200_pipeline_run_host(ccglib_b200_pipeline *pipeline
 CCGLIB_B200_API size_t ccglib_b200_pipeline_host_slice(const ccglib_b200_pipeline *pipeline);
 CCGLIB_B200_API int ccglib_b200_pipeline_set_host_slice(ccglib_b200_pipeline *pipeline, size_t items);
 
+/* With the opt variant and a batch of several chunks (chunks of at least 2e13 operations, at most
+ * eight), ccglib_b200_pipeline_run puts the transposes on an internal side stream, chunk by chunk,
+ * so that those of later chunks run beside the GEMM of earlier ones; the caller still sees one
+ * in-order stream.  on = 0 keeps the plain chain (all transposes, then one GEMM) on the caller's
+ * stream; the environment variable CCGLIB_B200_PIPE_OVERLAP=0 does the same at creation.
+ * No counterpart in the reference. */
+CCGLIB_B200_API int ccglib_b200_pipeline_set_overlap(ccglib_b200_pipeline *pipeline, int on);
+
 /* Benchmark hook: two caller-owned CUDA events (CUevent / cudaEvent_t values) that every
  * later run records on the run's stream just before and just after the GEMM stage of the chain
  * (for 1-bit input the stage includes the operand expansion); NULL, NULL switches it off.

@@ -109,6 +109,41 @@ def test_f16_pipeline_device_operands(in_axis):
     pipe.close()
 
 
+@pytest.mark.parametrize("chunk", ["1", "2", "3"])
+def test_f16_pipeline_chunks_overlap_transposes_and_gemm(chunk, monkeypatch):
+    """With several chunks the transposes run on the pipeline's side stream beside the GEMM of
+    earlier chunks; results are those of the single-chunk chain, call after call (the second call
+    must not transpose into buffers the first call's GEMMs are still reading)."""
+    import torch
+
+    B, M, N, K = 7, 300, 264, 200
+    rng = np.random.default_rng(55)
+    a = ou.random_storage(rng, (B, 2, M, K), ou.F16, "uniform")
+    b = ou.random_storage(rng, (B, 2, N, K), ou.F16, "uniform")
+    a2 = ou.random_storage(rng, (B, 2, M, K), ou.F16, "uniform")
+    d_a, d_b, d_a2 = gu.dev(_interleave(a)), gu.dev(_interleave(b)), gu.dev(_interleave(a2))
+    monkeypatch.setenv("CCGLIB_B200_PIPE_CHUNK", chunk)
+    pipe = capi.Pipeline(B, M, N, K, ou.F16, ou.F32, variant=capi.OPT,
+                         input_complex_axis=capi.INTERLEAVED)
+    chunks = -(-B // int(chunk))
+    assert pipe.launches == 3 * chunks
+    pipe.set_overlap(False)
+    assert pipe.launches == 3
+    pipe.set_overlap(True)
+    d_c1 = gu.dev_empty(B * 2 * M * N * 4, 0xEE)
+    d_c2 = gu.dev_empty(B * 2 * M * N * 4, 0xEE)
+    side = torch.cuda.Stream()  # a non-blocking caller stream
+    with torch.cuda.stream(side):
+        pipe.run(d_a.data_ptr(), d_b.data_ptr(), d_c1.data_ptr(), int(side.cuda_stream))
+        pipe.run(d_a2.data_ptr(), d_b.data_ptr(), d_c2.data_ptr(), int(side.cuda_stream))
+    side.synchronize()  # only the caller's stream
+    gu.check_device_status()
+    for d_c, aa in ((d_c1, a), (d_c2, a2)):
+        got = gu.host(d_c, np.float32).reshape(B, 2, M, N)
+        gu.assert_close_fp64(got, ou.F16, ou.F32, aa, b, K)
+    pipe.close()
+
+
 def _pinned(x):
     import torch
 
