@@ -219,3 +219,38 @@ def test_pipeline_rejects_what_it_cannot_do():
     with pytest.raises(capi.Error):
         pipe.host_slice = 3
     pipe.close()
+
+
+def test_create_destroy_returns_all_device_memory():
+    """Plans and pipelines own scratch, streams and events; creating, running and destroying
+    them many times must leave the device's free memory where it was."""
+    import torch
+
+    B, M, N, K = 4, 256, 256, 512
+    a, b = _bytes_inputs(56, B, M, N, K)
+    d_a, d_b = gu.dev(a), gu.dev(b)
+    d_c = gu.dev_empty(B * 2 * M * N * 4)
+    h_c = np.zeros(B * 2 * M * N, np.int32)
+    torch.cuda.synchronize()
+
+    def cycle():
+        pipe = capi.Pipeline(B, M, N, K, ou.INT1, ou.INT32)
+        pipe.host_slice = 2
+        pipe.run(d_a.data_ptr(), d_b.data_ptr(), d_c.data_ptr(), gu.stream_handle())
+        pipe.run_host(a.ctypes.data, b.ctypes.data, h_c.ctypes.data, gu.stream_handle())
+        pipe.close()
+        fp = capi.Pipeline(B, M, N, K, ou.F16, ou.F32, input_complex_axis=capi.INTERLEAVED)
+        fp.close()
+        plan = capi.GemmPlan(B, M, N, K, ou.INT1, ou.INT32, variant=capi.BASIC)
+        plan.close()
+
+    cycle()  # first use loads modules and creates the context's pools
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(25):
+        cycle()
+    torch.cuda.synchronize()
+    free_after = torch.cuda.mem_get_info()[0]
+    assert free_before - free_after < (8 << 20), "device memory leaked: %d bytes" % (
+        free_before - free_after)
+    gu.check_device_status()
