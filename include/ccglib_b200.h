@@ -191,7 +191,10 @@ typedef struct ccglib_b200_pipeline_desc {
 
 typedef struct ccglib_b200_pipeline ccglib_b200_pipeline;
 
-/* Validates, creates the GEMM plan and allocates the tiled buffers of the device path.
+/* A pipeline owns its scratch and internal streams: like the reference's objects it is not
+ * thread-safe and must not run on two streams at the same time.
+ *
+ * Validates, creates the GEMM plan and allocates the tiled buffers of the device path.
  * Replaces Pipeline::Impl::Impl (reference src/pipeline/Pipeline.cpp:44-106). */
 CCGLIB_B200_API int ccglib_b200_pipeline_create(const ccglib_b200_pipeline_desc *desc,
                                                 ccglib_b200_pipeline **pipeline);
