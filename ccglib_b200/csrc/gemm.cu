@@ -413,8 +413,13 @@ int ccglib_b200::create_gemm_plan(const ccglib_b200_gemm_desc *desc, const PlanO
   const bool short_k = plan.k_bytes <= 2048;
   const double cost_128 = static_cast<double>(ceil_div(tiles_m * ceil_div<size_t>(d.n, 128), sms)) *
                           (short_k ? 1.0 : 1.05);
+  // (short rows of 32-bit input are the exception: twice the operand bytes per flop make the
+  // narrow tile's extra traffic from L2 cost more, in time and under the power cap in clock,
+  // than the wide tile's exposed epilogue: 518 against 479-507 TFLOP/s sustained on
+  // 256 x 2048 x 512 tf32)
+  const double wide_short = in_bits >= 32 ? 0.97 : 1.06;
   const double cost_256 = static_cast<double>(ceil_div(tiles_m * ceil_div<size_t>(d.n, 256), sms)) *
-                          2.0 * (short_k ? 1.06 : 1.0);
+                          2.0 * (short_k ? wide_short : 1.0);
   // 64-column tiles double the tile count once more for problems that cannot fill the SMs (a
   // single 1024^3 product is 64 tiles of 128 x 128: 466 against 419 TFLOP/s).
   const double cost_64 = static_cast<double>(ceil_div(tiles_m * ceil_div<size_t>(d.n, 64), sms)) *

@@ -450,12 +450,25 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   const uint32_t bar_empty = bar_full + 8 * kStages;
   const uint32_t bar_acc_full = bar_empty + 8 * kStages;
   const uint32_t bar_acc_empty = bar_acc_full + 8 * kAccStages;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 2 * kAccStages);
+  const uint32_t bar_borrow = bar_acc_empty + 8 * kAccStages;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 2 * kAccStages + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   const uint32_t smem_base = smem_u32(smem);
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
+
+  // With one accumulator stage the epilogue is exposed: the MMAs of the next tile wait for it.
+  // Its speed is set by how many TMA stores a warp may have in flight, i.e. by staging space, so
+  // for the tile's epilogue the warps borrow the pipeline stage that the tile's last k-block
+  // used (free once the accumulator is complete): six staging tiles per warp instead of two.
+  // The producer's next load into that stage (k-block kStages - 1 of the next tile) waits until
+  // the stores have read it (bar_borrow); the next tile's first k-blocks sit in the other stages
+  // and were prefetched during the epilogue.
+  constexpr int kBorrowDepth = 6;
+  constexpr bool BORROW = EPI_TMA && kAccStages == 1 && KIND != kKindMXF4 &&
+                          C::kStageBytes >= 4 * kBorrowDepth * kStagingTile;
+  const bool borrow = BORROW && p.epi_tma && p.k_blocks >= static_cast<uint32_t>(kStages);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -466,6 +479,7 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       mbar_init(bar_acc_full + 8 * s, 1);
       mbar_init(bar_acc_empty + 8 * s, 4);  // one arrival per epilogue warp
     }
+    mbar_init(bar_borrow, 4);  // one arrival per epilogue warp and tile
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&tm_a);
@@ -536,13 +550,22 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     if (lane == 0) {
       for (uint32_t i = 0; i < p.prefetch; ++i) prefetch_next();
     }
-    for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+    uint32_t tile_iter = 0;
+    for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tile_iter) {
       const TileCoord t = decode_tile(p, tile);
       for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
         if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status,
                        kDevTimeoutProducer, p.wait_cycles)) {
           ok = false;
           break;
+        }
+        if (borrow && tile_iter > 0 && kb == static_cast<uint32_t>(kStages - 1)) {
+          // this stage was the previous tile's last one: its epilogue staged C in it
+          if (!mbar_wait(bar_borrow, (tile_iter - 1) & 1, abort_flag, p.status,
+                         kDevTimeoutProducer, p.wait_cycles)) {
+            ok = false;
+            break;
+          }
         }
         if (lane == 0) {
           int32_t ax, ay, az, bx, by, bz;
@@ -676,6 +699,19 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         tmem_wait_ld();
         if constexpr (EPI_TMA) {
           if (p.epi_tma) {
+            if constexpr (BORROW) {
+              if (borrow) {
+                // the stage of this tile's last k-block (global k-block (iter + 1) * k_blocks - 1)
+                const uint32_t last_stage = static_cast<uint32_t>(
+                    (static_cast<uint64_t>(iter + 1) * p.k_blocks - 1) % kStages);
+                const uint32_t staging = smem_base + last_stage * C::kStageBytes +
+                                         quad * (kBorrowDepth * kStagingTile);
+                epilogue_chunk_staged<OutT, kBorrowDepth>(p, &tm_c, staging, slot, lane, t.b,
+                                                          t.mt * kBlockM + quad * 32, n0, bits_re,
+                                                          bits_im);
+                continue;
+              }
+            }
             const uint32_t staging =
                 smem_base + kStages * C::kStageBytes + quad * (EPI * kStagingTile);
             epilogue_chunk_staged<OutT, (EPI > 0 ? EPI : 2)>(p, &tm_c, staging, slot, lane, t.b,
@@ -690,6 +726,16 @@ cgemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       __syncwarp();
       if (warp == 2 && lane == 0) CCGLIB_TRACE(iter, 3);
       if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+      if constexpr (BORROW) {
+        if (borrow) {
+          // hand the borrowed stage back once this warp's stores have read it
+          if (lane == 0) {
+            bulk_wait_group_read<0>();
+            mbar_arrive(bar_borrow);
+          }
+          __syncwarp();
+        }
+      }
       if (++acc == kAccStages) {
         acc = 0;
         acc_phase ^= 1;
