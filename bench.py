@@ -76,7 +76,12 @@ TYPE_BITS = {0: 1, 1: 32, 2: 16, 3: 8, 4: 8, 5: 16, 6: 32}
 # captures of small cases (dram__bytes_read.sum + dram__bytes_write.sum; batch items are walked
 # one after another, so the traffic grows in proportion to the batch).  Workloads without a
 # capture report null.
-NCU_DRAM_BYTES_PER_ITEM = {"c2_f16_opt_8192_b64": 3.39e9}
+NCU_DRAM_BYTES_PER_ITEM = {
+    "c2_f16_opt_8192_b64": 3.39e9,          # 6.79 GB for a 2-item launch
+    "c3_int1_4096_k65536_b32": 1.625e9,     # GEMM kernel alone: 3.25 GB for a 2-item launch
+    "c4_e4m3_4096_k16384_b32": 0.8525e9,    # 3.41 GB for a 4-item launch
+    "c5_bf16_256x2048x512_b4096": 9.18e6,   # 4.70 GB for a 512-item launch (= algorithmic)
+}
 C1_ROTATE = 16  # config 1 (16 MiB per problem) rotates over 16 operand sets: 256 MiB > L2
 
 
@@ -583,8 +588,8 @@ def roofline_of(name, dtype, M, N, K, bits, items, gemm_ms, peaks):
         "frac": achieved / peak,
         "traffic": (NCU_DRAM_BYTES_PER_ITEM[name] * items
                     if name in NCU_DRAM_BYTES_PER_ITEM else None),
-        "traffic_source": ("single-launch ncu capture of a 2-item case, scaled by the batch"
-                           if name in NCU_DRAM_BYTES_PER_ITEM else
+        "traffic_source": ("single-launch ncu capture of a small case of the GEMM kernel, scaled "
+                           "by the batch" if name in NCU_DRAM_BYTES_PER_ITEM else
                            "no ncu capture of this workload's kernel is wired in"),
         "algorithmic_bytes": items * (2.0 * (M + N) * K * bits / 8 + 2.0 * M * N * 4),
         "peak_source": "%s sustained bf16 GEMM x %.2g (nominal dtype rate ratio%s)" % (
