@@ -254,3 +254,37 @@ def test_create_destroy_returns_all_device_memory():
     assert free_before - free_after < (8 << 20), "device memory leaked: %d bytes" % (
         free_before - free_after)
     gu.check_device_status()
+
+
+@pytest.mark.parametrize("in_axis", [capi.PLANAR, capi.INTERLEAVED], ids=["planar", "interleaved"])
+def test_int1_byte_samples_at_an_odd_address(in_axis):
+    """Byte samples need no alignment: from an address that is not a multiple of 16 the front end
+    reads sample by sample instead of in 16-byte pieces and gives the same result."""
+    import torch
+
+    B, M, N, K = 2, 72, 40, 1024
+    a, b = _bytes_inputs(57, B, M, N, K)
+    want = gu.oracle_batch(ou.INT1, ou.INT32, _packed(a), _packed(b), B, M, N, K)
+    a_in = _interleave(a) if in_axis == capi.INTERLEAVED else a
+    b_in = _interleave(b) if in_axis == capi.INTERLEAVED else b
+    d_a = gu.dev_empty(a_in.size + 16, 0)
+    d_b = gu.dev_empty(b_in.size + 16, 0)
+    d_a[3:3 + a_in.size] = gu.dev(a_in)
+    d_b[5:5 + b_in.size] = gu.dev(b_in)
+    d_c = gu.dev_empty(B * 2 * M * N * 4, 0xEE)
+    pipe = capi.Pipeline(B, M, N, K, ou.INT1, ou.INT32, input_complex_axis=in_axis)
+    pipe.run(d_a.data_ptr() + 3, d_b.data_ptr() + 5, d_c.data_ptr(), gu.stream_handle())
+    torch.cuda.synchronize()
+    gu.check_device_status()
+    pipe.close()
+    assert np.array_equal(gu.host(d_c, np.int32).reshape(B, 2, M, N), want)
+
+
+def test_misaligned_float_operands_are_rejected():
+    """TMA needs 16-byte aligned operands; the GEMM says so instead of faulting."""
+    d = gu.dev_empty(1 << 20, 0)
+    plan = capi.GemmPlan(1, 128, 128, 128, ou.F16, ou.F32, variant=capi.BASIC)
+    with pytest.raises(capi.Error) as err:
+        plan.run(d.data_ptr() + 2, d.data_ptr(), d.data_ptr() + (1 << 19), gu.stream_handle())
+    assert err.value.status == capi.INVALID_ARGUMENT and "16-byte aligned" in str(err.value)
+    plan.close()
